@@ -1,0 +1,490 @@
+// C ABI of the sm_100a attention library: argument validation, launch plans,
+// TMA tensor maps and kernel launches.  Nothing here allocates device memory or
+// synchronises a stream (except the explicit status query); scratch is provided
+// by the caller and sized by the *_workspace_bytes functions.
+#include "../../include/arc_sdpa.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "decode_sm100.cuh"
+#include "prefill_sm100.cuh"
+
+namespace arc {
+
+// Per-device status word written by kernels whose bounded waits give up.
+__device__ uint32_t g_fault_words[2];
+
+constexpr int kMaxDevices = 64;
+// The decode kernel keeps a few bytes of static shared memory; the dynamic part
+// may use the opt-in maximum minus this reserve.
+constexpr int kDecodeStaticSmem = 1024;
+
+struct DeviceState {
+    bool ready = false;
+    uint32_t* fault = nullptr;
+    int sm_count = 0;
+    int smem_optin = 0;
+};
+
+static DeviceState g_dev[kMaxDevices];
+static std::mutex g_mu;
+static std::atomic<uint64_t> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+// Text of the most recent failing CUDA call on this thread (for diagnostics).
+static thread_local char g_last_error[256] = "";
+
+static int cuda_fail(const char* what, cudaError_t e) {
+    std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    cudaGetLastError();
+    return ARC_ERR_CUDA;
+}
+
+#define ARC_CUDA(call)                                      \
+    do {                                                    \
+        cudaError_t e_ = (call);                            \
+        if (e_ != cudaSuccess) return cuda_fail(#call, e_); \
+    } while (0)
+
+template <typename K>
+static cudaError_t opt_in_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+// One-time set-up for the current device: status-word address, SM count, and the
+// dynamic shared memory opt-in of every kernel.
+static int device_state(DeviceState** out) {
+    int dev = 0;
+    ARC_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return ARC_ERR_CUDA;
+    DeviceState& s = g_dev[dev];
+    if (!s.ready) {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!s.ready) {
+            void* sym = nullptr;
+            ARC_CUDA(cudaGetSymbolAddress(&sym, g_fault_words));
+            s.fault = static_cast<uint32_t*>(sym);
+            ARC_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev));
+            ARC_CUDA(cudaDeviceGetAttribute(&s.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+            if (!g_encode) {
+                void* fn = nullptr;
+                cudaDriverEntryPointQueryResult qres = cudaDriverEntryPointSymbolNotFound;
+                ARC_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+                if (qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+                    std::snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled not found in the driver");
+                    return ARC_ERR_CUDA;
+                }
+                g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+            }
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 1>, s.smem_optin - kDecodeStaticSmem));
+            ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
+            ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
+            ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 2>, s.smem_optin - kDecodeStaticSmem));
+            s.ready = true;
+        }
+    }
+    *out = &s;
+    return ARC_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// (hd, heads, tokens, batch) view of a token-major bf16 tensor; box = 64 x 1 x 128 x 1, 128-byte swizzle.
+static int make_tile_map(CUtensorMap* tm, const void* base, int hd, int heads, int tokens, int batch,
+                         int64_t stride_t, int64_t stride_b) {
+    cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
+    cuuint64_t sb = (cuuint64_t)(batch > 1 ? stride_b : stride_t * (int64_t)tokens) * 2u;
+    cuuint64_t strides[3] = {(cuuint64_t)hd * 2u, (cuuint64_t)stride_t * 2u, sb};
+    cuuint32_t box[4] = {64u, 1u, 128u, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        std::snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return ARC_ERR_CUDA;
+    }
+    return ARC_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Prefill plan
+// ---------------------------------------------------------------------------
+struct PrefillPlan {
+    int q_tiles = 0;
+    int splits = 1;
+    long long rows = 0;
+    size_t ws_bytes = 0;
+};
+
+static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillPlan* plan) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    if (p->batch <= 0 || p->seq <= 0 || p->kv_len <= 0 || p->nq <= 0 || p->nkv <= 0 || p->nq % p->nkv != 0)
+        return ARC_ERR_BAD_SHAPE;
+    if (p->hd != 128 && p->hd != 256) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
+    if (!(p->scale > 0.f) || !std::isfinite(p->scale)) return ARC_ERR_BAD_SHAPE;
+    if (p->mask_type != ARC_MASK_NONE && p->mask_type != ARC_MASK_EXPLICIT && p->mask_type != ARC_MASK_CAUSAL)
+        return ARC_ERR_BAD_SHAPE;
+    if (p->num_splits < 0) return ARC_ERR_BAD_SHAPE;
+    if ((long long)p->batch * p->nq > 65535LL * 64) return ARC_ERR_TOO_LARGE;
+    plan->q_tiles = (p->seq + 127) / 128;
+    plan->rows = (long long)p->batch * p->seq * p->nq;
+    const int kv_blocks = (p->kv_len + 127) / 128;
+    int splits = p->num_splits;
+    if (splits == 0) {
+        // Split the key range only when the tiles alone leave most SMs idle.
+        const long long tiles = (long long)plan->q_tiles * p->nq * p->batch;
+        splits = 1;
+        if (tiles * 2 <= sm_count && kv_blocks >= 4) {
+            splits = (int)(sm_count / tiles);
+            if (splits > kv_blocks / 2) splits = kv_blocks / 2;
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (splits > kv_blocks) splits = kv_blocks;
+    if (splits > 64) splits = 64;
+    if ((long long)p->batch * splits > 65535) return ARC_ERR_TOO_LARGE;
+    plan->splits = splits;
+    plan->ws_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
+    return ARC_OK;
+}
+
+template <int HD>
+static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& plan, DeviceState* ds,
+                          cudaStream_t stream) {
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tile_map(&tq, p->q, HD, p->nq, p->seq, p->batch, p->q_stride_t, p->q_stride_b)) != ARC_OK) return rc;
+    if ((rc = make_tile_map(&tk, p->k, HD, p->nkv, p->kv_len, p->batch, p->k_stride_t, p->k_stride_b)) != ARC_OK) return rc;
+    if ((rc = make_tile_map(&tv, p->v, HD, p->nkv, p->kv_len, p->batch, p->v_stride_t, p->v_stride_b)) != ARC_OK) return rc;
+
+    PrefillParams kp{};
+    kp.out = static_cast<uint16_t*>(p->out);
+    kp.gate = static_cast<const uint16_t*>(p->gate);
+    kp.mask = p->mask_type == ARC_MASK_EXPLICIT ? p->mask : nullptr;
+    kp.out_lse = p->out_lse;
+    kp.part_o = static_cast<float*>(p->workspace);
+    kp.part_lse = kp.part_o ? kp.part_o + (size_t)plan.splits * plan.rows * HD : nullptr;
+    kp.fault = ds->fault;
+    kp.batch = p->batch;
+    kp.seq = p->seq;
+    kp.kv_len = p->kv_len;
+    kp.nq = p->nq;
+    kp.nkv = p->nkv;
+    kp.o_stride_b = p->o_stride_b;
+    kp.o_stride_t = p->o_stride_t;
+    kp.scale_log2 = p->scale * 1.4426950408889634f;
+    kp.mask_type = p->mask_type;
+    kp.window = p->window;
+    kp.num_splits = plan.splits;
+
+    dim3 grid((unsigned)plan.q_tiles, (unsigned)p->nq, (unsigned)(p->batch * plan.splits));
+    sdpa_prefill_kernel<HD><<<grid, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    ARC_CUDA(cudaGetLastError());
+
+    if (plan.splits > 1) {
+        UniformMergeParams mp{};
+        mp.part_o = kp.part_o;
+        mp.part_lse = kp.part_lse;
+        mp.gate = kp.gate;
+        mp.out = kp.out;
+        mp.out_f32 = nullptr;
+        mp.out_lse = p->out_lse;
+        mp.rows = plan.rows;
+        mp.num_parts = plan.splits;
+        mp.seq = p->seq;
+        mp.nq = p->nq;
+        mp.o_stride_b = p->o_stride_b;
+        mp.o_stride_t = p->o_stride_t;
+        sdpa_uniform_merge_kernel<HD><<<(unsigned)plan.rows, HD / 2, 0, stream>>>(mp);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        ARC_CUDA(cudaGetLastError());
+    }
+    return ARC_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Decode plan
+// ---------------------------------------------------------------------------
+struct DecodePlan {
+    int nkv_cta = 1, groups = 1, slices = 1, stages = 2, ncta = 1, nt = 1;
+    int smem_bytes = 0;
+    long long parts = 0;
+    size_t ws_bytes = 0;
+};
+
+static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_optin, DecodePlan* plan) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    if (p->batch <= 0 || p->nq <= 0 || p->nkv <= 0 || p->nq % p->nkv != 0) return ARC_ERR_BAD_SHAPE;
+    if (p->batch > DECODE_MAX_BATCH) return ARC_ERR_TOO_LARGE;
+    if (p->hd != 128 && p->hd != 256) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
+    if (!(p->scale > 0.f) || !std::isfinite(p->scale)) return ARC_ERR_BAD_SHAPE;
+    if (!p->kv_len && p->kv_len_uniform < 0) return ARC_ERR_BAD_SHAPE;
+    const int G = p->nq / p->nkv;
+    if (G > 16) return ARC_ERR_UNSUPPORTED_GQA;
+    plan->nt = G > 8 ? 2 : 1;
+    // Heads per CTA: the largest divisor of nkv whose row (all its heads) is <= 2 KB.
+    const int max_heads = 1024 / p->hd;  // 8 for hd 128, 4 for hd 256
+    int nkv_cta = 1;
+    for (int c = 1; c <= p->nkv && c <= max_heads; ++c)
+        if (p->nkv % c == 0) nkv_cta = c;
+    plan->nkv_cta = nkv_cta;
+    plan->groups = p->nkv / nkv_cta;
+    const int pitch = nkv_cta * p->hd * 2 + 16;
+    int slices = (68 * 1024) / (32 * pitch);
+    if (slices > 8 / nkv_cta) slices = 8 / nkv_cta;
+    if (slices < 1) slices = 1;
+    plan->slices = slices;
+    const int stage_bytes = 2 * 16 * slices * pitch;
+    const int fixed = 128 + 2 * 8 * 8 + (p->batch + 2) * 8;
+    int stages = (smem_optin - kDecodeStaticSmem - fixed) / stage_bytes;
+    if (stages > 4) stages = 4;
+    if (stages < 2) return ARC_ERR_TOO_LARGE;
+    plan->stages = stages;
+    plan->smem_bytes = stages * stage_bytes + fixed;
+    int ncta = p->num_ctas > 0 ? p->num_ctas : sm_count / plan->groups;
+    if (ncta < 1) ncta = 1;
+    plan->ncta = ncta;
+    plan->parts = ((long long)ncta + p->batch) * slices;
+    plan->ws_bytes = (size_t)plan->parts * p->nq * ((size_t)p->hd + 1) * sizeof(float);
+    return ARC_OK;
+}
+
+template <int HD>
+static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan, DeviceState* ds,
+                         cudaStream_t stream) {
+    DecodeParams kp{};
+    kp.q = static_cast<const uint16_t*>(p->q);
+    kp.k = static_cast<const uint16_t*>(p->k);
+    kp.v = static_cast<const uint16_t*>(p->v);
+    kp.kv_len = p->kv_len;
+    kp.kv_row_offset = reinterpret_cast<const long long*>(p->kv_row_offset);
+    kp.part_o = static_cast<float*>(p->workspace);
+    kp.part_lse = kp.part_o + (size_t)plan.parts * p->nq * HD;
+    kp.fault = ds->fault;
+    kp.batch = p->batch;
+    kp.nq = p->nq;
+    kp.nkv = p->nkv;
+    kp.kv_len_uniform = p->kv_len_uniform;
+    kp.q_stride_b = p->q_stride_b;
+    kp.kv_stride_b = p->kv_stride_b;
+    kp.kv_stride_t = p->kv_stride_t;
+    kp.scale_log2 = p->scale * 1.4426950408889634f;
+    kp.nkv_cta = plan.nkv_cta;
+    kp.slices = plan.slices;
+    kp.stages = plan.stages;
+    kp.ncta = plan.ncta;
+
+    dim3 grid((unsigned)plan.ncta, (unsigned)plan.groups, 1);
+    const unsigned threads = 32u * (unsigned)(plan.nkv_cta * plan.slices + 1);
+    if (plan.nt == 1)
+        sdpa_decode_kernel<HD, 1><<<grid, threads, plan.smem_bytes, stream>>>(kp);
+    else
+        sdpa_decode_kernel<HD, 2><<<grid, threads, plan.smem_bytes, stream>>>(kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    ARC_CUDA(cudaGetLastError());
+
+    DecodeMergeParams mp{};
+    mp.part_o = kp.part_o;
+    mp.part_lse = kp.part_lse;
+    mp.kv_len = p->kv_len;
+    mp.gate = static_cast<const uint16_t*>(p->gate);
+    mp.out = static_cast<uint16_t*>(p->out);
+    mp.out_f32 = p->out_f32;
+    mp.out_lse = p->out_lse;
+    mp.batch = p->batch;
+    mp.nq = p->nq;
+    mp.kv_len_uniform = p->kv_len_uniform;
+    mp.ncta = plan.ncta;
+    mp.slices = plan.slices;
+    mp.o_stride_b = p->o_stride_b;
+    dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
+    sdpa_decode_merge_kernel<HD><<<mgrid, HD / 2, (size_t)(p->batch + 2) * 8, stream>>>(mp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    ARC_CUDA(cudaGetLastError());
+    return ARC_OK;
+}
+
+}  // namespace arc
+
+// ===========================================================================
+// extern "C"
+// ===========================================================================
+using namespace arc;
+
+extern "C" const char* arc_sdpa_status_string(int status) {
+    switch (status) {
+        case ARC_OK: return "ok";
+        case ARC_ERR_BAD_SHAPE: return "bad shape or parameter";
+        case ARC_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+        case ARC_ERR_UNSUPPORTED_HEAD_DIM: return "head_dim must be 128 or 256";
+        case ARC_ERR_WORKSPACE_TOO_SMALL: return "workspace missing or too small";
+        case ARC_ERR_CUDA: return "CUDA call failed";
+        case ARC_ERR_COLLECTIVE: return "collective failed";
+        case ARC_ERR_DEVICE_WAIT_TIMEOUT: return "a bounded device-side wait gave up";
+        case ARC_ERR_NULL_POINTER: return "required pointer is null";
+        case ARC_ERR_UNSUPPORTED_GQA: return "more than 16 query heads per KV head";
+        case ARC_ERR_TOO_LARGE: return "size beyond a fixed limit";
+        default: return "unknown status";
+    }
+}
+
+extern "C" size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params* p) {
+    DeviceState* ds = nullptr;
+    int sm = 148;
+    if (device_state(&ds) == ARC_OK) sm = ds->sm_count;
+    PrefillPlan plan;
+    if (plan_prefill(p, sm, &plan) != ARC_OK) return 0;
+    return plan.ws_bytes;
+}
+
+extern "C" int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    if (!p->q || !p->k || !p->v || !p->out) return ARC_ERR_NULL_POINTER;
+    if (p->mask_type == ARC_MASK_EXPLICIT && !p->mask) return ARC_ERR_NULL_POINTER;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc != ARC_OK) return rc;
+    PrefillPlan plan;
+    if ((rc = plan_prefill(p, ds->sm_count, &plan)) != ARC_OK) return rc;
+    if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
+        (p->gate && !aligned16(p->gate)))
+        return ARC_ERR_ALIGNMENT;
+    const int64_t strides[8] = {p->q_stride_b, p->q_stride_t, p->k_stride_b, p->k_stride_t,
+                                p->v_stride_b, p->v_stride_t, p->o_stride_b, p->o_stride_t};
+    for (int64_t s : strides)
+        if (s < 0 || (s & 7) != 0) return ARC_ERR_ALIGNMENT;
+    if (p->q_stride_t < (int64_t)p->nq * p->hd || p->o_stride_t < (int64_t)p->nq * p->hd ||
+        p->k_stride_t < (int64_t)p->nkv * p->hd || p->v_stride_t < (int64_t)p->nkv * p->hd)
+        return ARC_ERR_BAD_SHAPE;
+    if (plan.splits > 1) {
+        if (!p->workspace || p->workspace_bytes < plan.ws_bytes) return ARC_ERR_WORKSPACE_TOO_SMALL;
+        if (!aligned16(p->workspace)) return ARC_ERR_ALIGNMENT;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return p->hd == 128 ? launch_prefill<128>(p, plan, ds, st) : launch_prefill<256>(p, plan, ds, st);
+}
+
+extern "C" size_t arc_sdpa_decode_workspace_bytes(const arc_sdpa_decode_params* p) {
+    DeviceState* ds = nullptr;
+    if (device_state(&ds) != ARC_OK) return 0;
+    DecodePlan plan;
+    if (plan_decode(p, ds->sm_count, ds->smem_optin, &plan) != ARC_OK) return 0;
+    return plan.ws_bytes;
+}
+
+extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    if (!p->q || !p->k || !p->v) return ARC_ERR_NULL_POINTER;
+    if (!p->out && !p->out_f32) return ARC_ERR_NULL_POINTER;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc != ARC_OK) return rc;
+    DecodePlan plan;
+    if ((rc = plan_decode(p, ds->sm_count, ds->smem_optin, &plan)) != ARC_OK) return rc;
+    if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || (p->out && !aligned16(p->out)) ||
+        (p->gate && !aligned16(p->gate)) || (p->out_f32 && !aligned16(p->out_f32)))
+        return ARC_ERR_ALIGNMENT;
+    if ((p->q_stride_b & 7) || (p->o_stride_b & 7) || (p->kv_stride_t & 7) || p->kv_stride_t < (int64_t)p->nkv * p->hd ||
+        p->q_stride_b < 0 || p->o_stride_b < 0 || p->kv_stride_b < 0)
+        return ARC_ERR_ALIGNMENT;
+    if (p->gate && !p->out) return ARC_ERR_NULL_POINTER;
+    if (!p->workspace || p->workspace_bytes < plan.ws_bytes) return ARC_ERR_WORKSPACE_TOO_SMALL;
+    if (!aligned16(p->workspace)) return ARC_ERR_ALIGNMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return p->hd == 128 ? launch_decode<128>(p, plan, ds, st) : launch_decode<256>(p, plan, ds, st);
+}
+
+extern "C" int arc_sdpa_merge(const float* part_out, const float* part_lse, int32_t num_parts, int64_t rows,
+                              int32_t hd, const void* gate, void* out_bf16, float* out_f32, float* out_lse,
+                              void* stream) {
+    if (!part_out || !part_lse) return ARC_ERR_NULL_POINTER;
+    if (!out_bf16 && !out_f32) return ARC_ERR_NULL_POINTER;
+    if (num_parts <= 0 || rows <= 0 || rows > 0x7fffffffLL) return ARC_ERR_BAD_SHAPE;
+    if (hd != 128 && hd != 256) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
+    if (gate && !out_bf16) return ARC_ERR_NULL_POINTER;
+    if (!aligned16(part_out) || (out_bf16 && !aligned16(out_bf16)) || (out_f32 && !aligned16(out_f32)) ||
+        (gate && !aligned16(gate)))
+        return ARC_ERR_ALIGNMENT;
+    UniformMergeParams mp{};
+    mp.part_o = part_out;
+    mp.part_lse = part_lse;
+    mp.gate = static_cast<const uint16_t*>(gate);
+    mp.out = static_cast<uint16_t*>(out_bf16);
+    mp.out_f32 = out_f32;
+    mp.out_lse = out_lse;
+    mp.rows = rows;
+    mp.num_parts = num_parts;
+    mp.seq = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (hd == 128)
+        sdpa_uniform_merge_kernel<128><<<(unsigned)rows, 64, 0, st>>>(mp);
+    else
+        sdpa_uniform_merge_kernel<256><<<(unsigned)rows, 128, 0, st>>>(mp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
+}
+
+extern "C" int arc_mul_sigmoid_inplace(void* a, const void* gate, int64_t n, void* stream) {
+    if (!a || !gate) return ARC_ERR_NULL_POINTER;
+    if (n < 0) return ARC_ERR_BAD_SHAPE;
+    if (n == 0) return ARC_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    mul_sigmoid_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(a), static_cast<const uint16_t*>(gate), n);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
+}
+
+extern "C" int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,
+                                    int32_t sliding_window, void* stream) {
+    if (!mask) return ARC_ERR_NULL_POINTER;
+    if (q_len < 0 || kv_len < 0) return ARC_ERR_BAD_SHAPE;
+    const long long n = (long long)q_len * kv_len;
+    if (n == 0) return ARC_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    fill_causal_mask_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(mask, q_len, kv_len,
+                                                                                            past_offset, sliding_window);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
+}
+
+extern "C" int arc_sdpa_device_status(uint32_t* fault_code, uint32_t* fault_detail) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc != ARC_OK) return rc;
+    uint32_t w[2] = {0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return ARC_ERR_CUDA;
+    if (cudaMemcpy(w, ds->fault, sizeof(w), cudaMemcpyDeviceToHost) != cudaSuccess) return ARC_ERR_CUDA;
+    if (fault_code) *fault_code = w[0];
+    if (fault_detail) *fault_detail = w[1];
+    return w[0] == 0 ? ARC_OK : ARC_ERR_DEVICE_WAIT_TIMEOUT;
+}
+
+extern "C" int arc_sdpa_clear_device_status(void) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc != ARC_OK) return rc;
+    if (cudaDeviceSynchronize() != cudaSuccess) return ARC_ERR_CUDA;
+    return cudaMemset(ds->fault, 0, 2 * sizeof(uint32_t)) == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
+}
+
+extern "C" const char* arc_sdpa_last_error(void) { return g_last_error; }
+
+extern "C" uint64_t arc_sdpa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

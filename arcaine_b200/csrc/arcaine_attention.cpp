@@ -1,0 +1,158 @@
+// Reference-shaped C++ wrappers over the C ABI (see arcaine_attention.hpp).
+#include "arcaine_attention.hpp"
+
+#include <stdexcept>
+#include <string>
+
+#include "../../include/arc_sdpa.h"
+
+namespace arcaine {
+
+namespace {
+
+void throw_on(int status, const char* where) {
+    if (status != ARC_OK)
+        throw std::runtime_error(std::string(where) + ": " + arc_sdpa_status_string(status));
+}
+
+// One sequence, token-major contiguous tensors: (tokens, heads, hd).
+void run_prefill(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v, bf16* out, const bf16* gate,
+                 const float* mask, int seq, int kv_len, int nq, int nkv, int hd, float scale, int mask_type,
+                 int window, SdpaWorkspace& ws, const char* where) {
+    arc_sdpa_prefill_params p{};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.out = out;
+    p.gate = gate;
+    p.mask = mask;
+    p.batch = 1;
+    p.seq = seq;
+    p.kv_len = kv_len;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.hd = hd;
+    p.q_stride_t = p.o_stride_t = (int64_t)nq * hd;
+    p.k_stride_t = p.v_stride_t = (int64_t)nkv * hd;
+    p.q_stride_b = p.o_stride_b = (int64_t)seq * nq * hd;
+    p.k_stride_b = p.v_stride_b = (int64_t)kv_len * nkv * hd;
+    p.scale = scale;
+    p.mask_type = mask_type;
+    p.window = window;
+    p.num_splits = 0;
+    const size_t need = arc_sdpa_prefill_workspace_bytes(&p);
+    if (need) {
+        p.workspace = ws.reserve(need);
+        p.workspace_bytes = ws.capacity();
+    }
+    throw_on(arc_sdpa_prefill(&p, stream), where);
+}
+
+void run_decode(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v, bf16* out, const bf16* gate,
+                int kv_len, int nq, int nkv, int hd, float scale, SdpaWorkspace& ws, const char* where) {
+    arc_sdpa_decode_params p{};
+    p.q = q;
+    p.k = k;
+    p.v = v;
+    p.out = out;
+    p.gate = gate;
+    p.batch = 1;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.hd = hd;
+    p.kv_len_uniform = kv_len;
+    p.max_kv_len = kv_len;
+    p.q_stride_b = p.o_stride_b = (int64_t)nq * hd;
+    p.kv_stride_b = kv_len;
+    p.kv_stride_t = (int64_t)nkv * hd;
+    p.scale = scale;
+    const size_t need = arc_sdpa_decode_workspace_bytes(&p);
+    if (need == 0) throw_on(arc_sdpa_decode(&p, stream), where);  // reports the reason
+    p.workspace = ws.reserve(need);
+    p.workspace_bytes = ws.capacity();
+    throw_on(arc_sdpa_decode(&p, stream), where);
+}
+
+}  // namespace
+
+SdpaWorkspace::~SdpaWorkspace() {
+    if (ptr_) cudaFree(ptr_);
+}
+
+void* SdpaWorkspace::reserve(size_t bytes) {
+    if (bytes > bytes_) {
+        if (ptr_) cudaFree(ptr_);
+        ptr_ = nullptr;
+        bytes_ = 0;
+        if (cudaMalloc(&ptr_, bytes) != cudaSuccess) throw std::runtime_error("SdpaWorkspace: cudaMalloc failed");
+        bytes_ = bytes;
+    }
+    return ptr_;
+}
+
+void gqa_attention_sdpa(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, const bf16* Kc,
+                        const bf16* Vc, int kv_len, int nkv, const float* mask, int mask_type, bf16* out,
+                        SdpaWorkspace& ws) {
+    run_prefill(ctx.stream, Q, Kc, Vc, out, nullptr, mask, seq, kv_len, nq, nkv, hd, 1.0f, mask_type,
+                ARC_NO_WINDOW, ws, "gqa_attention_sdpa");
+}
+
+void gqa_attention(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, const bf16* Kc, const bf16* Vc,
+                   int kv_len, int nkv, int /*past_offset*/, int sliding_window, bool causal, bf16* out,
+                   SdpaWorkspace& ws) {
+    // Query and key positions share past_offset, so it cancels out of the rule.
+    run_prefill(ctx.stream, Q, Kc, Vc, out, nullptr, nullptr, seq, kv_len, nq, nkv, hd, 1.0f,
+                causal ? ARC_MASK_CAUSAL : ARC_MASK_NONE, causal ? sliding_window : ARC_NO_WINDOW, ws,
+                "gqa_attention");
+}
+
+void batched_attention(CudaEngine& ctx, const bf16* Q_dev, int seq_len, int nq_heads, int q_head_dim,
+                       const bf16* K_dev, const bf16* V_dev, int kv_len, int nkv_heads, int kv_head_dim,
+                       int /*past_offset*/, int sliding_window, float scale, bool skip_mask,
+                       const int32_t* block_ids, bf16* out, SdpaWorkspace& ws) {
+    if (block_ids) throw std::runtime_error("batched_attention: vision block ids are not supported");
+    if (q_head_dim != kv_head_dim) throw std::runtime_error("batched_attention: q and kv head_dim differ");
+    run_prefill(ctx.stream, Q_dev, K_dev, V_dev, out, nullptr, nullptr, seq_len, kv_len, nq_heads, nkv_heads,
+                q_head_dim, scale, skip_mask ? ARC_MASK_NONE : ARC_MASK_CAUSAL,
+                skip_mask ? ARC_NO_WINDOW : sliding_window, ws, "batched_attention");
+}
+
+void qwen35_xmx_attention(cudaStream_t stream, const bf16* query, const bf16* key, const bf16* value,
+                          bf16* output, int seq, int past, int query_heads, int key_heads, int head_dim,
+                          float scale, SdpaWorkspace& ws) {
+    if (key_heads <= 0 || query_heads % key_heads != 0)
+        throw std::runtime_error("Qwen3.5 attention requires integral GQA ratio");
+    if (seq == 1)
+        run_decode(stream, query, key, value, output, nullptr, past + 1, query_heads, key_heads, head_dim, scale,
+                   ws, "qwen35_xmx_attention");
+    else
+        run_prefill(stream, query, key, value, output, nullptr, nullptr, seq, past + seq, query_heads, key_heads,
+                    head_dim, scale, ARC_MASK_CAUSAL, ARC_NO_WINDOW, ws, "qwen35_xmx_attention");
+}
+
+void qwen35_online_attention(cudaStream_t stream, const bf16* query, const bf16* key, const bf16* value,
+                             bf16* output, int seq, int past, int query_heads, int key_heads, int head_dim,
+                             float scale, SdpaWorkspace& ws) {
+    qwen35_xmx_attention(stream, query, key, value, output, seq, past, query_heads, key_heads, head_dim, scale, ws);
+}
+
+void qwen35_xmx_attention_decode_gqa(cudaStream_t stream, const bf16* query, const bf16* key,
+                                     const bf16* value, bf16* output, int past, int query_heads,
+                                     int key_heads, int head_dim, float scale, const bf16* gate,
+                                     SdpaWorkspace& ws) {
+    if (key_heads <= 0 || query_heads % key_heads != 0)
+        throw std::runtime_error("Qwen3.5 attention requires integral GQA ratio");
+    run_decode(stream, query, key, value, output, gate, past + 1, query_heads, key_heads, head_dim, scale, ws,
+               "qwen35_xmx_attention_decode_gqa");
+}
+
+void mul_sigmoid_inplace(cudaStream_t stream, bf16* a, const bf16* gate, size_t n) {
+    throw_on(arc_mul_sigmoid_inplace(a, gate, (int64_t)n, stream), "mul_sigmoid_inplace");
+}
+
+void fill_causal_mask(cudaStream_t stream, float* mask, int q_len, int kv_len, int past_offset,
+                      int sliding_window) {
+    throw_on(arc_fill_causal_mask(mask, q_len, kv_len, past_offset, sliding_window, stream), "fill_causal_mask");
+}
+
+}  // namespace arcaine

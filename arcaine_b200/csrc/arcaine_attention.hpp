@@ -1,0 +1,93 @@
+// C++ host interface of the attention path, shaped like the reference's own
+// free functions so a call site changes its context type and nothing else:
+// raw device pointers to bf16-as-uint16_t, int dimensions, enqueue-only on the
+// engine's stream, std::runtime_error on failure.  Every function forwards to
+// the C ABI in include/arc_sdpa.h; there is no other backend and no CPU path.
+//
+//   reference                                              here
+//   GpuEngine {engine, stream, queue, index}               CudaEngine {index, stream}
+//     (src/common/gpu/engine.hpp:10-19)
+//   diffarena::Alloc<bf16> result from the per-GPU arena   caller-provided `out`
+//     (src/modeling/diffusion_gemma/attention.cpp:940-942)
+#pragma once
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cstddef>
+#include <cstdint>
+
+namespace arcaine {
+
+using bf16 = uint16_t;  // raw bits, src/common/gpu/buffer.hpp:8
+
+// Stand-in for GpuEngine: which GPU, and the in-order stream work is enqueued on.
+struct CudaEngine {
+    int index = 0;
+    cudaStream_t stream = nullptr;
+};
+
+// Grow-only device scratch for split-KV partials.  The reference learned that
+// per-call allocation costs throughput (persistent attention scratch, notes/
+// diffusion_gemma/NVFP4_DPAS_KERNEL.md:243-250); this buffer reallocates only
+// when a call needs more than any call before it.
+class SdpaWorkspace {
+public:
+    SdpaWorkspace() = default;
+    ~SdpaWorkspace();
+    SdpaWorkspace(const SdpaWorkspace&) = delete;
+    SdpaWorkspace& operator=(const SdpaWorkspace&) = delete;
+    void* reserve(size_t bytes);  // throws std::runtime_error on allocation failure
+    size_t capacity() const { return bytes_; }
+
+private:
+    void* ptr_ = nullptr;
+    size_t bytes_ = 0;
+};
+
+// src/modeling/diffusion_gemma/attention.cpp:930-995.  O = softmax(Q K^T + mask) V,
+// no scale (Q and K arrive RMS-normed), GQA with nkv KV heads.  mask_type: 0 none,
+// 1 explicit additive f32 (seq, kv_len), 3 causal aligned bottom-right.
+void gqa_attention_sdpa(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, const bf16* Kc,
+                        const bf16* Vc, int kv_len, int nkv, const float* mask, int mask_type, bf16* out,
+                        SdpaWorkspace& ws);
+
+// src/modeling/diffusion_gemma/attention.cpp:706-821.  Same result through inline
+// causal / sliding-window masking: query i sits at absolute position
+// past_offset + i, key 0 at past_offset - (kv_len - seq).
+void gqa_attention(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, const bf16* Kc, const bf16* Vc,
+                   int kv_len, int nkv, int past_offset, int sliding_window, bool causal, bf16* out,
+                   SdpaWorkspace& ws);
+
+// src/common/layers/attention_batched.hpp:71-136.  scores*scale + causal/window
+// mask (skip_mask: no mask).  Vision block ids are not supported (throws).
+void batched_attention(CudaEngine& ctx, const bf16* Q_dev, int seq_len, int nq_heads, int q_head_dim,
+                       const bf16* K_dev, const bf16* V_dev, int kv_len, int nkv_heads, int kv_head_dim,
+                       int past_offset, int sliding_window, float scale, bool skip_mask,
+                       const int32_t* block_ids, bf16* out, SdpaWorkspace& ws);
+
+// src/modeling/qwen3_5/kernels.hpp:621-679 / 761-905.  Causal GQA attention of
+// `seq` new tokens over a cache holding past + seq positions; `output` may alias
+// `query`.  seq == 1 takes the split-KV decode kernel, seq > 1 the prefill kernel.
+void qwen35_xmx_attention(cudaStream_t stream, const bf16* query, const bf16* key, const bf16* value,
+                          bf16* output, int seq, int past, int query_heads, int key_heads, int head_dim,
+                          float scale, SdpaWorkspace& ws);
+void qwen35_online_attention(cudaStream_t stream, const bf16* query, const bf16* key, const bf16* value,
+                             bf16* output, int seq, int past, int query_heads, int key_heads, int head_dim,
+                             float scale, SdpaWorkspace& ws);
+
+// src/modeling/qwen3_5/kernels.hpp:910-1054 (single-token decode), with the
+// sigmoid output gate of src/modeling/qwen3_5/operators.hpp:160 optionally fused
+// (gate == nullptr: plain attention).
+void qwen35_xmx_attention_decode_gqa(cudaStream_t stream, const bf16* query, const bf16* key,
+                                     const bf16* value, bf16* output, int past, int query_heads,
+                                     int key_heads, int head_dim, float scale, const bf16* gate,
+                                     SdpaWorkspace& ws);
+
+// src/modeling/qwen3_5_moe/kernels.hpp:80-88
+void mul_sigmoid_inplace(cudaStream_t stream, bf16* a, const bf16* gate, size_t n);
+
+// src/common/kernels/attention_mask.hpp:12-38
+void fill_causal_mask(cudaStream_t stream, float* mask, int q_len, int kv_len, int past_offset,
+                      int sliding_window);
+
+}  // namespace arcaine

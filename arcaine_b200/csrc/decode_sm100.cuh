@@ -1,0 +1,488 @@
+// HBM-bound split-KV decode kernel for sm_100a, plus the log-sum-exp merges.
+//
+// One new query token per sequence attends to that sequence's contiguous KV
+// cache rows of (nkv, hd) bf16 (the reference's per-layer cache,
+// src/modeling/qwen3_5/cache.hpp:9-14).  The key ranges of all sequences are
+// laid end to end and cut into one equal share per CTA (persistent grid, one CTA
+// per SM), so the load is balanced whatever the per-sequence lengths are and a
+// CTA streams one long contiguous run of cache rows.
+//
+// Inside a CTA a producer warp issues one 16-byte-aligned bulk async copy per
+// cache row (all KV heads of the CTA's head group: nkv_cta*hd*2 contiguous
+// bytes) into a ring of shared-memory stages; rows are padded by 16 bytes so
+// ldmatrix reads are bank-conflict free.  Consumer warps each own one KV head
+// and a 16-key slice of every stage.  The GQA group of that head (<= 8 query
+// heads per n-tile) forms the N dimension of the warp MMAs, so K and V are read
+// from HBM and from shared memory exactly once per group:
+//     S^T (16 keys x 8 heads) = K_tile (16 x hd) * Q^T (hd x 8)
+//     O^T (hd x 8 heads)     += V_tile^T (hd x 16) * P^T (16 x 8)
+// Online softmax state (max, sum) is per head = per accumulator column pair,
+// reduced across the key rows with warp shuffles.  Each (CTA, sequence) pair a
+// share touches yields one partial (normalised out, lse) record per slice; the
+// merge kernel folds them and applies the optional sigmoid output gate
+// (src/modeling/qwen3_5_moe/kernels.hpp:80-88) while writing bf16.
+//
+// The reference kernels this replaces read K/V once per query head and never
+// split the key range (src/modeling/qwen3_5/kernels.hpp:761-905), or fold the
+// group into the MMA rows but launch only nkv*4 work-groups (:910-1054).
+#pragma once
+#include <math_constants.h>
+
+#include "ptx.cuh"
+
+namespace arc {
+
+constexpr int DECODE_MAX_BATCH = 2048;
+
+struct DecodeParams {
+    const uint16_t* q;
+    const uint16_t* k;
+    const uint16_t* v;
+    const int* kv_len;
+    const long long* kv_row_offset;
+    float* part_o;    // [(slot * slices + slice)][nq][HD]
+    float* part_lse;  // [(slot * slices + slice)][nq]
+    uint32_t* fault;
+    int batch, nq, nkv, kv_len_uniform;
+    long long q_stride_b, kv_stride_b, kv_stride_t;
+    float scale_log2;
+    int nkv_cta;  // KV heads handled by one CTA (grid.y = nkv / nkv_cta)
+    int slices;   // 16-key slices per stage; consumer warps = nkv_cta * slices
+    int stages;
+    int ncta;     // grid.x
+};
+
+// Prefix sums of the per-sequence lengths into shared memory: cum[b] = keys
+// before sequence b, cum[batch] = total.  Called by every thread of the block.
+__device__ __forceinline__ void build_len_prefix(const int* kv_len, int kv_len_uniform, int batch,
+                                                 long long* cum) {
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+        int len = kv_len ? kv_len[b] : kv_len_uniform;
+        cum[b + 1] = len > 0 ? len : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        long long run = 0;
+        cum[0] = 0;
+        for (int b = 0; b < batch; ++b) {
+            run += cum[b + 1];
+            cum[b + 1] = run;
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ long long share_size(long long total, int ncta, int tile_keys) {
+    long long per = (total + ncta - 1) / ncta;
+    per = (per + tile_keys - 1) / tile_keys * tile_keys;
+    return per > 0 ? per : tile_keys;
+}
+
+template <int HD, int NT>
+__global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+
+    const int ncw = p.nkv_cta * p.slices;  // consumer warps
+    const int tk = 16 * p.slices;          // keys per stage
+    const int row_bytes = p.nkv_cta * HD * 2;
+    const int pitch = row_bytes + 16;
+    const int tile_bytes = tk * pitch;  // one of K / V
+    const int stage_bytes = 2 * tile_bytes;
+
+    uint8_t* stage_base = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
+    uint64_t* empty = full + p.stages;
+    long long* cum = reinterpret_cast<long long*>(empty + p.stages);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int head0 = blockIdx.y * p.nkv_cta;  // first KV head of this CTA
+    const int G = p.nq / p.nkv;
+
+    // A fault recorded by an earlier CTA or launch: do not start new waits.
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile uint32_t*>(p.fault);
+    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
+    if (abort_flag != 0u) return;
+    const long long total = cum[p.batch];
+    const long long per = share_size(total, p.ncta, tk);
+    const long long g0 = (long long)blockIdx.x * per;
+    const long long g1 = min(total, g0 + per);
+
+    // Zero the staging ring so rows a short tile leaves unwritten hold finite data.
+    {
+        uint4* z = reinterpret_cast<uint4*>(stage_base);
+        const int n16 = p.stages * stage_bytes / 16;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], ncw);
+        }
+        fence_mbar_init();
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (g0 >= g1) return;
+
+    int b_first = 0;
+    while (b_first < p.batch - 1 && cum[b_first + 1] <= g0) ++b_first;
+
+    if (warp == ncw) {
+        // ------------------------------------------------------------------ producer
+        int it = 0;
+        bool ok = true;
+        int b = b_first;
+        long long g = g0;
+        while (ok && g < g1) {
+            while (cum[b + 1] <= g) ++b;
+            const long long seg_end = min(g1, cum[b + 1]);
+            const long long row0 = (p.kv_row_offset ? p.kv_row_offset[b] : (long long)b * p.kv_stride_b) + (g - cum[b]);
+            const int seg_keys = (int)(seg_end - g);
+            for (int k0 = 0; k0 < seg_keys; k0 += tk, ++it) {
+                const int st = it % p.stages;
+                if (it >= p.stages && !mbar_wait_warp(&empty[st], ((it / p.stages) - 1) & 1)) {
+                    if (lane == 0) report_fault(p.fault, FAULT_WAIT_EMPTY, it);
+                    ok = false;
+                    break;
+                }
+                const int nk = min(tk, seg_keys - k0);
+                if (lane == 0) mbar_arrive_expect_tx(&full[st], (uint32_t)(2 * nk * row_bytes));
+                __syncwarp();
+                uint8_t* dstK = stage_base + (size_t)st * stage_bytes;
+                for (int r = lane; r < 2 * nk; r += 32) {
+                    const int is_v = r >= nk;
+                    const int key = r - is_v * nk;
+                    const uint16_t* src = (is_v ? p.v : p.k) + (row0 + k0 + key) * p.kv_stride_t + (long long)head0 * HD;
+                    bulk_load_1d(dstK + (size_t)is_v * tile_bytes + (size_t)key * pitch, src, (uint32_t)row_bytes,
+                                 &full[st]);
+                }
+            }
+            g = seg_end;
+        }
+        // Drain: every copy issued above has landed before the CTA retires.
+        if (lane == 0) {
+            for (int back = 1; back <= p.stages && back <= it; ++back) {
+                const int j = it - back;
+                mbar_wait(&full[j % p.stages], (j / p.stages) & 1);
+            }
+        }
+    } else if (warp < ncw) {
+        // ------------------------------------------------------------------ consumers
+        const int hl = warp % p.nkv_cta;  // local KV head
+        const int slice = warp / p.nkv_cta;
+        const int kvh = head0 + hl;
+        const int g4 = lane >> 2;  // accumulator row group
+        const int q4 = lane & 3;   // accumulator column pair
+        const float sl = p.scale_log2;
+
+        int it = 0;
+        bool ok = true;
+        int b = b_first;
+        long long g = g0;
+        while (ok && g < g1) {
+            while (cum[b + 1] <= g) ++b;
+            const long long seg_end = min(g1, cum[b + 1]);
+            const int seg_keys = (int)(seg_end - g);
+
+            // Q^T fragments (B operand, hd x 8 heads) for this head's GQA group.
+            uint32_t qf[NT][HD / 16][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int n = nt * 8 + g4;
+                const bool valid = n < G;
+                const uint16_t* qp = p.q + (long long)b * p.q_stride_b + ((long long)kvh * G + (valid ? n : 0)) * HD + q4 * 2;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    qf[nt][kk][0] = valid ? *reinterpret_cast<const uint32_t*>(qp + kk * 16) : 0u;
+                    qf[nt][kk][1] = valid ? *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8) : 0u;
+                }
+            }
+            float m[NT][2], l[NT][2];
+            float o[NT][HD / 16][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                m[nt][0] = m[nt][1] = -CUDART_INF_F;
+                l[nt][0] = l[nt][1] = 0.f;
+#pragma unroll
+                for (int mt = 0; mt < HD / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.f;
+            }
+
+            for (int k0 = 0; k0 < seg_keys; k0 += tk, ++it) {
+                const int st = it % p.stages;
+                if (!mbar_wait_warp(&full[st], (it / p.stages) & 1)) {
+                    if (lane == 0) report_fault(p.fault, FAULT_WAIT_FULL, it);
+                    ok = false;
+                    break;
+                }
+                const int nk = min(tk, seg_keys - k0);
+                const int nvalid = min(16, nk - slice * 16);  // keys of this warp's slice
+                if (nvalid > 0) {
+                    const uint32_t sK = smem_u32(stage_base + (size_t)st * stage_bytes) + (slice * 16) * pitch + hl * HD * 2;
+                    const uint32_t sV = sK + tile_bytes;
+                    const uint32_t a_k = sK + (lane & 15) * pitch + (lane >> 4) * 16;
+                    const uint32_t a_v = sV + ((lane & 7) + (lane >> 4) * 8) * pitch + ((lane >> 3) & 1) * 16;
+
+                    float acc[NT][2][4];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) acc[nt][hh][0] = acc[nt][hh][1] = acc[nt][hh][2] = acc[nt][hh][3] = 0.f;
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        uint32_t a[4];
+                        ldmatrix_x4(a, a_k + kk * 32);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(acc[nt][kk & 1], a, qf[nt][kk][0], qf[nt][kk][1]);
+                    }
+                    const bool v_lo = g4 < nvalid, v_hi = g4 + 8 < nvalid;
+                    uint32_t pb[NT][2];
+                    bool any_rescale = false;
+                    float alpha[NT][2];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        float x[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float s = (acc[nt][0][e] + acc[nt][1][e]) * sl;
+                            x[e] = ((e < 2) ? v_lo : v_hi) ? s : -CUDART_INF_F;
+                        }
+                        float pr[4];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            float mx = fmaxf(x[u], x[u + 2]);
+                            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                            const float m_new = fmaxf(m[nt][u], mx);
+                            const float m_eff = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+                            alpha[nt][u] = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m[nt][u] - m_new);
+                            pr[u] = fast_exp2(x[u] - m_eff);
+                            pr[u + 2] = fast_exp2(x[u + 2] - m_eff);
+                            l[nt][u] = l[nt][u] * alpha[nt][u] + pr[u] + pr[u + 2];
+                            m[nt][u] = m_new;
+                            any_rescale |= alpha[nt][u] != 1.f;
+                        }
+                        pb[nt][0] = movmatrix_trans(pack_bf16x2(pr[0], pr[1]));
+                        pb[nt][1] = movmatrix_trans(pack_bf16x2(pr[2], pr[3]));
+                    }
+                    if (__any_sync(0xffffffffu, any_rescale)) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int mt = 0; mt < HD / 16; ++mt) {
+                                o[nt][mt][0] *= alpha[nt][0];
+                                o[nt][mt][1] *= alpha[nt][1];
+                                o[nt][mt][2] *= alpha[nt][0];
+                                o[nt][mt][3] *= alpha[nt][1];
+                            }
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < HD / 16; ++mt) {
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(a, a_v + mt * 32);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(o[nt][mt], a, pb[nt][0], pb[nt][1]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);
+            }
+
+            // Partial record of this (CTA, sequence, slice): normalised out + natural-log lse.
+            if (ok) {
+                const long long part = ((long long)blockIdx.x + b) * p.slices + slice;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float inv[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        float ls = l[nt][u];
+                        ls += __shfl_xor_sync(0xffffffffu, ls, 4);
+                        ls += __shfl_xor_sync(0xffffffffu, ls, 8);
+                        ls += __shfl_xor_sync(0xffffffffu, ls, 16);
+                        inv[u] = ls > 0.f ? 1.f / ls : 0.f;
+                        const int n = nt * 8 + q4 * 2 + u;
+                        if (g4 == 0 && n < G)
+                            p.part_lse[part * p.nq + (long long)kvh * G + n] =
+                                ls > 0.f ? (m[nt][u] + fast_log2(ls)) * 0.6931471805599453f : -CUDART_INF_F;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int n = nt * 8 + q4 * 2 + u;
+                        if (n < G) {
+                            float* dst = p.part_o + (part * p.nq + (long long)kvh * G + n) * HD;
+#pragma unroll
+                            for (int mt = 0; mt < HD / 16; ++mt) {
+                                dst[mt * 16 + g4] = o[nt][mt][u] * inv[u];
+                                dst[mt * 16 + g4 + 8] = o[nt][mt][u + 2] * inv[u];
+                            }
+                        }
+                    }
+                }
+            }
+            g = seg_end;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Merge of the decode partials.  grid = (nq, batch); the block recomputes the
+// same share boundaries the decode kernel used to find the records of its
+// sequence: CTAs [c_first, c_last] x slices, record index (cta + b)*slices + s.
+// ---------------------------------------------------------------------------
+struct DecodeMergeParams {
+    const float* part_o;
+    const float* part_lse;
+    const int* kv_len;
+    const uint16_t* gate;
+    uint16_t* out;
+    float* out_f32;
+    float* out_lse;
+    int batch, nq, kv_len_uniform;
+    int ncta, slices;
+    long long o_stride_b;
+};
+
+__device__ __forceinline__ float sigmoid_gate(float attn, uint16_t gate_bits) {
+    const float g = bf16_bits_to_f32(gate_bits);
+    return bf16_round(attn) * (1.0f / (1.0f + __expf(-g)));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD / 2) sdpa_decode_merge_kernel(const DecodeMergeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    long long* cum = reinterpret_cast<long long*>(smem_raw);
+    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
+    const int h = blockIdx.x, b = blockIdx.y;
+    const long long total = cum[p.batch];
+    const long long per = share_size(total, p.ncta, 16 * p.slices);
+    const long long k_begin = cum[b], k_end = cum[b + 1];
+    const int d = threadIdx.x * 2;
+    float acc0 = 0.f, acc1 = 0.f, lse = -CUDART_INF_F;
+    if (k_end > k_begin) {
+        const int c_first = (int)(k_begin / per), c_last = (int)((k_end - 1) / per);
+        const int n_parts = (c_last - c_first + 1) * p.slices;
+        const long long part0 = ((long long)c_first + b) * p.slices;
+        float mx = -CUDART_INF_F;
+        for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, p.part_lse[(part0 + i) * p.nq + h]);
+        float z = 0.f;
+        if (mx > -CUDART_INF_F) {
+            for (int i = 0; i < n_parts; ++i) {
+                const float li = p.part_lse[(part0 + i) * p.nq + h];
+                if (li == -CUDART_INF_F) continue;
+                const float w = __expf(li - mx);
+                z += w;
+                const float2 ov = *reinterpret_cast<const float2*>(p.part_o + ((part0 + i) * p.nq + h) * HD + d);
+                acc0 = fmaf(w, ov.x, acc0);
+                acc1 = fmaf(w, ov.y, acc1);
+            }
+            const float inv = 1.f / z;
+            acc0 *= inv;
+            acc1 *= inv;
+            lse = mx + __logf(z);
+        }
+    }
+    const long long row = (long long)b * p.nq + h;
+    if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(acc0, acc1);
+    if (p.out_lse && threadIdx.x == 0) p.out_lse[row] = lse;
+    if (p.out) {
+        const long long eoff = (long long)b * p.o_stride_b + (long long)h * HD + d;
+        if (p.gate) {
+            const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff);
+            acc0 = sigmoid_gate(acc0, (uint16_t)(gw & 0xffffu));
+            acc1 = sigmoid_gate(acc1, (uint16_t)(gw >> 16));
+        }
+        *reinterpret_cast<uint32_t*>(p.out + eoff) = pack_bf16x2(acc0, acc1);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Merge of `num_parts` uniformly strided partial sets: part_o (parts, rows, hd),
+// part_lse (parts, rows).  One block per row.  Used for split prefill tiles and
+// for records gathered from other GPUs.  out rows are contiguous (rows, hd)
+// unless row_tokens > 0, in which case row = (b, t, h) is scattered with the
+// given strides (prefill output layout).
+// ---------------------------------------------------------------------------
+struct UniformMergeParams {
+    const float* part_o;
+    const float* part_lse;
+    const uint16_t* gate;
+    uint16_t* out;
+    float* out_f32;
+    float* out_lse;
+    long long rows;
+    int num_parts;
+    int seq, nq;  // seq > 0: strided (b, t, h) addressing of out / gate
+    long long o_stride_b, o_stride_t;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(HD / 2) sdpa_uniform_merge_kernel(const UniformMergeParams p) {
+    const long long row = blockIdx.x;
+    const int d = threadIdx.x * 2;
+    float mx = -CUDART_INF_F;
+    for (int i = 0; i < p.num_parts; ++i) mx = fmaxf(mx, p.part_lse[(long long)i * p.rows + row]);
+    float acc0 = 0.f, acc1 = 0.f, lse = -CUDART_INF_F;
+    if (mx > -CUDART_INF_F) {
+        float z = 0.f;
+        for (int i = 0; i < p.num_parts; ++i) {
+            const float li = p.part_lse[(long long)i * p.rows + row];
+            if (li == -CUDART_INF_F) continue;
+            const float w = __expf(li - mx);
+            z += w;
+            const float2 ov = *reinterpret_cast<const float2*>(p.part_o + ((long long)i * p.rows + row) * HD + d);
+            acc0 = fmaf(w, ov.x, acc0);
+            acc1 = fmaf(w, ov.y, acc1);
+        }
+        const float inv = 1.f / z;
+        acc0 *= inv;
+        acc1 *= inv;
+        lse = mx + __logf(z);
+    }
+    if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(acc0, acc1);
+    if (p.out_lse && threadIdx.x == 0) p.out_lse[row] = lse;
+    if (p.out) {
+        long long eoff = row * HD + d;
+        if (p.seq > 0) {
+            const long long hh = row % p.nq;
+            const long long t = (row / p.nq) % p.seq;
+            const long long bb = row / ((long long)p.nq * p.seq);
+            eoff = bb * p.o_stride_b + t * p.o_stride_t + hh * HD + d;
+        }
+        if (p.gate) {
+            const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff);
+            acc0 = sigmoid_gate(acc0, (uint16_t)(gw & 0xffffu));
+            acc1 = sigmoid_gate(acc1, (uint16_t)(gw >> 16));
+        }
+        *reinterpret_cast<uint32_t*>(p.out + eoff) = pack_bf16x2(acc0, acc1);
+    }
+}
+
+// a[i] = bf16(f32(a[i]) * sigmoid(f32(gate[i]))) : src/modeling/qwen3_5_moe/kernels.hpp:80-88
+__global__ void mul_sigmoid_kernel(uint16_t* a, const uint16_t* gate, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = bf16_bits_to_f32(gate[i]);
+        const float sig = 1.0f / (1.0f + __expf(-g));
+        a[i] = __bfloat16_as_ushort(__float2bfloat16_rn(bf16_bits_to_f32(a[i]) * sig));
+    }
+}
+
+// Additive causal / sliding-window mask : src/common/kernels/attention_mask.hpp:12-38
+__global__ void fill_causal_mask_kernel(float* mask, int q_len, int kv_len, int past_offset, int window) {
+    const long long n = (long long)q_len * kv_len;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int qi = (int)(i / kv_len), kvj = (int)(i % kv_len);
+        const int q_global = past_offset + qi;
+        const int kv_global = past_offset - (kv_len - q_len) + kvj;
+        const bool causal = kv_global > q_global;
+        const bool too_far = (window != 0x7fffffff) && (kv_global < q_global - window + 1);
+        mask[i] = (causal || too_far) ? -CUDART_INF_F : 0.0f;
+    }
+}
+
+}  // namespace arc

@@ -1,0 +1,420 @@
+// GQA flash-attention prefill / canvas kernel for sm_100a.
+//
+// One CTA owns a tile of 128 query tokens of one query head and walks the key
+// blocks (128 keys) that tile can see.  Q, K and V tiles are staged in shared
+// memory by TMA (128-byte swizzle, one 64-element column chunk per copy);
+// S = Q K^T and O += P V run on the tcgen05 tensor cores with both accumulators
+// in tensor memory; P is written back to tensor memory as bf16 over the S
+// columns and fed to the second MMA from there, so probabilities never touch
+// shared or global memory.  Softmax is online, fp32, one query row per thread.
+//
+// Warp roles (192 threads): warps 0-3 softmax + correction + epilogue (their
+// warp index selects the 32 TMEM lanes each may touch), warp 4 TMA producer and
+// TMEM owner, warp 5 MMA issuer.
+//
+// Masking follows the reference's rules evaluated inline instead of through a
+// (q_len, kv_len) f32 buffer: causal aligned bottom-right with an optional
+// window of the W most recent keys, self included
+// (src/common/kernels/attention_mask.hpp:12-38); no mask for the bidirectional
+// canvas-over-prompt call (src/modeling/diffusion_gemma/attention.cpp:1093-1103);
+// an explicit additive buffer is still accepted.  Key blocks wholly outside a
+// tile's visible band are never loaded (the band idea of gqa_attention,
+// src/modeling/diffusion_gemma/attention.cpp:721-769, per CTA).
+#pragma once
+#include <cuda.h>
+#include <math_constants.h>
+
+#include "ptx.cuh"
+
+namespace arc {
+
+struct PrefillParams {
+    uint16_t* out;
+    const uint16_t* gate;
+    const float* mask;
+    float* out_lse;
+    float* part_o;
+    float* part_lse;
+    uint32_t* fault;
+    int batch, seq, kv_len, nq, nkv;
+    long long o_stride_b, o_stride_t;
+    float scale_log2;  // scale * log2(e)
+    int mask_type, window;
+    int num_splits;
+};
+
+template <int HD>
+struct PrefillCfg {
+    static constexpr int BM = 128;  // query rows per CTA
+    static constexpr int BN = 128;  // keys per block
+    static constexpr int CH = HD / 64;
+    static constexpr int CHUNK_BYTES = 128 * 128;  // 128 rows x 64 bf16
+    static constexpr int TILE_BYTES = CH * CHUNK_BYTES;
+    static constexpr int TMEM_COLS = (HD == 128) ? 256 : 512;
+    static constexpr int COL_S = 0;    // 128 fp32 columns; P (bf16) aliases the first 64
+    static constexpr int COL_O = 128;  // HD fp32 columns
+    static constexpr int NUM_BARS = 8;
+    static constexpr int SMEM_BYTES = 3 * TILE_BYTES + NUM_BARS * 8 + 16 + 1024;
+    static constexpr int THREADS = 192;
+    static constexpr int MIN_CTAS = (HD == 128) ? 2 : 1;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_CTAS)
+    sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    using C = PrefillCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + C::TILE_BYTES;
+    uint8_t* sV = smem + 2 * C::TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * C::TILE_BYTES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = bars + 2;
+    uint64_t* v_full = bars + 3;
+    uint64_t* v_empty = bars + 4;
+    uint64_t* s_full = bars + 5;
+    uint64_t* p_full = bars + 6;
+    uint64_t* o_full = bars + 7;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
+    uint32_t* abort_slot = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int qt = blockIdx.x;
+    const int h = blockIdx.y;
+    const int b = blockIdx.z / p.num_splits;
+    const int split = blockIdx.z % p.num_splits;
+    const int kvh = h / (p.nq / p.nkv);
+    const int q0 = qt * C::BM;
+    const int off = p.kv_len - p.seq;
+    const bool causal = (p.mask_type == 3);
+    const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
+    const int q_last = min(q0 + C::BM - 1, p.seq - 1);
+
+    // Key blocks [blk_lo, blk_hi) this tile can see, then this split's share.
+    int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
+    if (causal) {
+        int last_key = min(p.kv_len - 1, q_last + off);
+        blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
+        if (windowed) blk_lo = max(0, q0 + off - p.window + 1) / C::BN;
+    }
+    const int nblk = max(0, blk_hi - blk_lo);
+    const int per = (nblk + p.num_splits - 1) / p.num_splits;
+    const int my_lo = blk_lo + split * per;
+    const int my_hi = min(blk_hi, my_lo + per);
+    const int n_my = max(0, my_hi - my_lo);
+
+    const long long rows_total = (long long)p.batch * p.seq * p.nq;
+
+    if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
+    __syncthreads();
+    if (*abort_slot) return;
+
+    if (n_my == 0) {
+        // Nothing visible: zero output (or an empty partial) for this tile.
+        if (warp < 4) {
+            const int t = q0 + threadIdx.x;
+            if (t < p.seq) {
+                const long long row = ((long long)b * p.seq + t) * p.nq + h;
+                if (p.num_splits > 1) {
+                    float4* dst = reinterpret_cast<float4*>(p.part_o + ((long long)split * rows_total + row) * HD);
+                    for (int i = 0; i < HD / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    p.part_lse[(long long)split * rows_total + row] = -CUDART_INF_F;
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD);
+                    for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
+                }
+            }
+        }
+        return;
+    }
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            prefetch_tensormap(&tm_q);
+            prefetch_tensormap(&tm_k);
+            prefetch_tensormap(&tm_v);
+            mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < C::CH; ++c) tma_load_4d(sQ + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, h, q0, b);
+            for (int i = 0; i < n_my; ++i) {
+                const int key0 = (my_lo + i) * C::BN;
+                if (i > 0 && !mbar_wait(k_empty, (i - 1) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u + i);
+                    break;
+                }
+                mbar_arrive_expect_tx(k_full, C::TILE_BYTES);
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c)
+                    tma_load_4d(sK + c * C::CHUNK_BYTES, &tm_k, k_full, c * 64, kvh, key0, b);
+                if (i > 0 && !mbar_wait(v_empty, (i - 1) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u + i);
+                    break;
+                }
+                mbar_arrive_expect_tx(v_full, C::TILE_BYTES);
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c)
+                    tma_load_4d(sV + c * C::CHUNK_BYTES, &tm_v, v_full, c * 64, kvh, key0, b);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
+            constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
+            const uint32_t tS = tmem_base + C::COL_S;
+            const uint32_t tO = tmem_base + C::COL_O;
+            const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) report_fault(p.fault, FAULT_WAIT_Q, 0);
+            for (int i = 0; ok && i < n_my; ++i) {
+                if (!mbar_wait(k_full, i & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_K, i);
+                    break;
+                }
+                tc_fence_after_sync();
+                // S = Q K^T : both operands K-major, 8-row groups 1024 bytes apart.
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t o = (kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32;
+                    umma_ss(tS, make_smem_desc_sw128(aQ + o, 16, 1024), make_smem_desc_sw128(aK + o, 16, 1024),
+                            IDESC_QK, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(k_empty);
+                umma_commit(s_full);
+                if (!mbar_wait(p_full, i & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_P, i);
+                    break;
+                }
+                if (!mbar_wait(v_full, i & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_V, i);
+                    break;
+                }
+                tc_fence_after_sync();
+                // O += P V : P from tensor memory (8 columns per 16 keys), V
+                // MN-major: 64-element head-dim chunks 16 KB apart (leading
+                // offset), 8-key groups 1024 bytes apart (stride offset).
+#pragma unroll
+                for (int ks = 0; ks < C::BN / 16; ++ks) {
+                    umma_ts(tO, tS + ks * 8, make_smem_desc_sw128(aV + ks * 2048, C::CHUNK_BYTES, 1024), IDESC_PV,
+                            (i > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(v_empty);
+            }
+            umma_commit(o_full);
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax / epilogue
+        const int r = threadIdx.x;
+        const int t = q0 + r;
+        const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t tS = tmem_base + lane_sel + C::COL_S;
+        const uint32_t tO = tmem_base + lane_sel + C::COL_O;
+        const float sl = p.scale_log2;
+        constexpr float LOG2E = 1.4426950408889634f;
+
+        int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
+        if (causal) {
+            const int diag = t + off;
+            row_hi = min(max(diag + 1, 0), p.kv_len);
+            if (windowed) row_lo = max(0, diag - p.window + 1);
+            if (row_lo > row_hi) row_lo = row_hi;
+        }
+        int tile_hi_min = p.kv_len, tile_lo_max = 0;
+        if (causal) {
+            tile_hi_min = min(max(q0 + off + 1, 0), p.kv_len);
+            if (windowed) tile_lo_max = max(0, q_last + off - p.window + 1);
+        }
+        const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
+        const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
+
+        float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
+        float l = 0.f;
+        bool ok = true;
+        uint32_t v[32];
+
+        for (int i = 0; i < n_my; ++i) {
+            const int key0 = (my_lo + i) * C::BN;
+            if (!mbar_wait_warp(s_full, i & 1)) {
+                report_fault(p.fault, FAULT_WAIT_S, i);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            const bool edge = has_mask || (key0 + C::BN > tile_hi_min) || (key0 < tile_lo_max);
+
+            // Pass 1: block maximum of this row.
+            float mx = -CUDART_INF_F;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(tS + c * 32, v);
+                tmem_wait_ld();
+                if (!edge) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int key = key0 + c * 32 + e;
+                        float x = __uint_as_float(v[e]) * sl;
+                        if (mask_row && key < p.kv_len) x += mask_row[key] * LOG2E;
+                        x = (key >= row_lo && key < row_hi) ? x : -CUDART_INF_F;
+                        mx = fmaxf(mx, x);
+                    }
+                }
+            }
+            const float m_blk = edge ? mx : mx * sl;
+            const float m_new = fmaxf(m, m_blk);
+            if (i == 0) {
+                m = m_new;
+            } else {
+                const bool need = m_new > m + 8.0f;
+                if (__any_sync(0xffffffffu, need)) {
+                    const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        tmem_ld32(tO + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                        tmem_st32(tO + c * 32, v);
+                    }
+                    l *= alpha;
+                    m = m_new;
+                }
+            }
+            const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+
+            // Pass 2: probabilities -> bf16 into the S columns, row sum in fp32.
+            float lsum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(tS + c * 32, v);
+                tmem_wait_ld();
+                uint32_t pk[16];
+                if (!edge) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, -m_eff));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
+                        lsum += p0 + p1;
+                        pk[e >> 1] = pack_bf16x2(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float pp[2];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const int key = key0 + c * 32 + e + u;
+                            float x = __uint_as_float(v[e + u]) * sl;
+                            if (mask_row && key < p.kv_len) x += mask_row[key] * LOG2E;
+                            x = (key >= row_lo && key < row_hi) ? x : -CUDART_INF_F;
+                            pp[u] = fast_exp2(x - m_eff);
+                        }
+                        lsum += pp[0] + pp[1];
+                        pk[e >> 1] = pack_bf16x2(pp[0], pp[1]);
+                    }
+                }
+                tmem_st16(tS + c * 16, pk);
+            }
+            l += lsum;
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(p_full);
+        }
+
+        if (ok && !mbar_wait_warp(o_full, 0)) {
+            report_fault(p.fault, FAULT_WAIT_O, 0);
+            ok = false;
+        }
+        tc_fence_after_sync();
+        if (ok) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
+            const long long row = ((long long)b * p.seq + t) * p.nq + h;
+            const bool store = t < p.seq;
+            if (p.num_splits > 1) {
+                float* dst = p.part_o + ((long long)split * rows_total + row) * HD;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    tmem_ld32(tO + c * 32, v);
+                    tmem_wait_ld();
+                    if (store) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<float4*>(dst + c * 32 + e) =
+                                make_float4(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv,
+                                            __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+                    }
+                }
+                if (store) p.part_lse[(long long)split * rows_total + row] = lse;
+            } else {
+                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD;
+                uint16_t* dst = p.out + eoff;
+                const uint16_t* g = p.gate ? p.gate + eoff : nullptr;
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    tmem_ld32(tO + c * 32, v);
+                    tmem_wait_ld();
+                    if (store) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            float o[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(v[e + u]) * inv;
+                            if (g) {
+                                const uint4 gv = *reinterpret_cast<const uint4*>(g + c * 32 + e);
+                                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
+                                    const float sig = 1.0f / (1.0f + __expf(-gf));
+                                    o[u] = bf16_round(o[u]) * sig;
+                                }
+                            }
+                            uint4 ov;
+                            ov.x = pack_bf16x2(o[0], o[1]);
+                            ov.y = pack_bf16x2(o[2], o[3]);
+                            ov.z = pack_bf16x2(o[4], o[5]);
+                            ov.w = pack_bf16x2(o[6], o[7]);
+                            *reinterpret_cast<uint4*>(dst + c * 32 + e) = ov;
+                        }
+                    }
+                }
+                if (store && p.out_lse) p.out_lse[row] = lse;
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+}  // namespace arc

@@ -1,0 +1,172 @@
+/*
+ * C ABI of the B200 (sm_100a) scaled-dot-product-attention library.
+ *
+ * These entry points are what a foreign-function binding of Arcaine's attention
+ * path would bind: plain pointers, sizes and a CUDA stream handle, `int` status
+ * returned, nothing thrown, nothing allocated and no synchronisation on the hot
+ * path (the reference's operators are enqueue-only too, src/common/gpu/ops.hpp:96
+ * "caller owns synchronization").
+ *
+ * Conventions shared by every call
+ *   - bf16 tensors are raw 16-bit patterns (the reference's `bf16 = uint16_t`,
+ *     src/common/gpu/buffer.hpp:8); all pointers are device pointers unless a
+ *     comment says otherwise, 16-byte aligned.
+ *   - token-major layouts of the reference: Q / O / gate (tokens, nq, hd),
+ *     K / V (positions, nkv, hd); strides below are in ELEMENTS and must be
+ *     multiples of 8.  The head stride is always `hd`.
+ *   - GQA: kv_head = q_head / (nq / nkv)
+ *     (src/common/layers/attention_layout.hpp:37-52, src/modeling/qwen3_5/kernels.hpp:637).
+ *   - score = (q . k) * scale + mask, softmax in fp32
+ *     (src/common/layers/attention_batched.hpp:28-44).
+ *   - `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef ARC_SDPA_H_
+#define ARC_SDPA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define ARC_OK 0
+#define ARC_ERR_BAD_SHAPE 1            /* non-positive size, nq % nkv != 0, ... */
+#define ARC_ERR_ALIGNMENT 2            /* pointer or stride not 16-byte aligned */
+#define ARC_ERR_UNSUPPORTED_HEAD_DIM 3 /* hd not in {128, 256} */
+#define ARC_ERR_WORKSPACE_TOO_SMALL 4
+#define ARC_ERR_CUDA 5                 /* a CUDA runtime / driver call failed */
+#define ARC_ERR_COLLECTIVE 6           /* reserved for the multi-GPU host layer */
+#define ARC_ERR_DEVICE_WAIT_TIMEOUT 7  /* a bounded device-side wait gave up */
+#define ARC_ERR_NULL_POINTER 8
+#define ARC_ERR_UNSUPPORTED_GQA 9      /* decode: more than 16 query heads per KV head */
+#define ARC_ERR_TOO_LARGE 10           /* size beyond a documented fixed limit */
+
+/* ---- mask types: the values the reference hands to oneDNN's sdpa
+ * (src/modeling/diffusion_gemma/attention.cpp:1032,1040,1099) -------------- */
+#define ARC_MASK_NONE 0     /* bidirectional: canvas queries over prompt + canvas */
+#define ARC_MASK_EXPLICIT 1 /* additive f32 buffer (seq, kv_len), shared by heads */
+#define ARC_MASK_CAUSAL 3   /* causal, aligned bottom-right; K may be longer than Q */
+#define ARC_NO_WINDOW 2147483647
+
+const char* arc_sdpa_status_string(int status);
+/* Text of the last failing CUDA call made by this thread inside the library
+ * (which call, and the CUDA error string); empty if none. */
+const char* arc_sdpa_last_error(void);
+
+/* -------------------------------------------------------------------------
+ * Prefill / canvas attention.  Replaces gqa_attention_sdpa
+ * (src/modeling/diffusion_gemma/attention.cpp:930-995), its matmul fallback
+ * gqa_attention (:706-821), batched_attention
+ * (src/common/layers/attention_batched.hpp:71-136) and the seq > 1 use of
+ * qwen35_xmx_attention (src/modeling/qwen3_5/kernels.hpp:761-905).
+ *
+ * With ARC_MASK_CAUSAL, `window` (ARC_NO_WINDOW = off) keeps only the `window`
+ * most recent keys, self included — the rule of fill_causal_mask
+ * (src/common/kernels/attention_mask.hpp:12-38) evaluated inline.
+ * `out` may alias `q` (the reference calls the Qwen kernel that way,
+ * src/modeling/qwen3_5/operators.hpp:143-147).
+ * `gate` (optional): out = bf16(attn) * sigmoid(gate), the fused form of
+ * mul_sigmoid_inplace (src/modeling/qwen3_5_moe/kernels.hpp:80-88).
+ * `num_splits` > 1 splits the key range over several CTAs per query tile and
+ * needs `workspace` of arc_sdpa_prefill_workspace_bytes(); 0 picks a value.
+ * ------------------------------------------------------------------------- */
+typedef struct arc_sdpa_prefill_params {
+    const void* q;     /* (batch, seq, nq, hd) bf16 */
+    const void* k;     /* (batch, kv_len, nkv, hd) bf16 */
+    const void* v;     /* (batch, kv_len, nkv, hd) bf16 */
+    void* out;         /* (batch, seq, nq, hd) bf16 */
+    const void* gate;  /* optional, laid out like out */
+    const float* mask; /* optional, (seq, kv_len) f32, ARC_MASK_EXPLICIT only */
+    float* out_lse;    /* optional, (batch, seq, nq) f32 natural-log softmax denominator */
+    int32_t batch, seq, kv_len, nq, nkv, hd;
+    int64_t q_stride_b, q_stride_t; /* elements */
+    int64_t k_stride_b, k_stride_t;
+    int64_t v_stride_b, v_stride_t;
+    int64_t o_stride_b, o_stride_t; /* also used for gate */
+    float scale;
+    int32_t mask_type;
+    int32_t window;
+    int32_t num_splits;
+    void* workspace;
+    size_t workspace_bytes;
+} arc_sdpa_prefill_params;
+
+size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params* p);
+int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream);
+
+/* -------------------------------------------------------------------------
+ * Split-KV decode: one new query token per sequence against a contiguous
+ * per-sequence KV cache (Qwen35KvLayerCache, src/modeling/qwen3_5/cache.hpp:9-14).
+ * Replaces the seq == 1 use of qwen35_xmx_attention / qwen35_online_attention
+ * (src/modeling/qwen3_5/kernels.hpp:621-679,761-905), the bench-only
+ * qwen35_xmx_attention_decode_gqa (:910-1054) and, with `gate`, the separate
+ * mul_sigmoid_inplace launch (src/modeling/qwen3_5/operators.hpp:160).
+ *
+ * The whole key range of the batch is cut into equal shares, one per CTA;
+ * partial (out, lse) records go through `workspace` and a merge kernel.
+ * Sequence b owns cache rows [row0_b, row0_b + kv_len_b) where row0_b is
+ * kv_row_offset[b] if given, else b * kv_stride_b.
+ * `out_f32` / `out_lse` (optional): unrounded, ungated attention output and
+ * natural-log LSE per (sequence, head), the record a sequence-sharded caller
+ * exchanges between GPUs before arc_sdpa_merge.
+ * ------------------------------------------------------------------------- */
+typedef struct arc_sdpa_decode_params {
+    const void* q;    /* (batch, nq, hd) bf16, batch stride q_stride_b */
+    const void* k;    /* rows of (nkv, hd) bf16 */
+    const void* v;
+    void* out;        /* (batch, nq, hd) bf16, batch stride o_stride_b; may be NULL */
+    const void* gate; /* optional, laid out like out */
+    const int32_t* kv_len;        /* device [batch]; NULL -> kv_len_uniform */
+    const int64_t* kv_row_offset; /* device [batch]; NULL -> b * kv_stride_b */
+    float* out_f32;               /* optional (batch, nq, hd) */
+    float* out_lse;               /* optional (batch, nq) */
+    int32_t batch, nq, nkv, hd;
+    int32_t kv_len_uniform;
+    int32_t max_kv_len; /* upper bound of any kv_len[b]; sizes nothing, validated only */
+    int64_t q_stride_b, o_stride_b; /* elements */
+    int64_t kv_stride_b;            /* rows between sequences (when kv_row_offset == NULL) */
+    int64_t kv_stride_t;            /* elements between consecutive rows (>= nkv*hd) */
+    float scale;
+    int32_t num_ctas; /* 0 -> one per SM */
+    void* workspace;
+    size_t workspace_bytes;
+} arc_sdpa_decode_params;
+
+size_t arc_sdpa_decode_workspace_bytes(const arc_sdpa_decode_params* p);
+int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream);
+
+/* -------------------------------------------------------------------------
+ * Log-sum-exp merge of `num_parts` partial results over disjoint key ranges
+ * (no counterpart in the reference, which never splits the key range):
+ *   lse = log sum_c exp(lse_c),  out = sum_c exp(lse_c - lse) * o_c.
+ * part_out (num_parts, rows, hd) f32, part_lse (num_parts, rows) f32.
+ * Outputs (each optional): out_bf16 (rows, hd) with the optional sigmoid gate
+ * (rows, hd) bf16 applied, out_f32 (rows, hd) ungated, out_lse (rows).
+ * ------------------------------------------------------------------------- */
+int arc_sdpa_merge(const float* part_out, const float* part_lse, int32_t num_parts, int64_t rows,
+                   int32_t hd, const void* gate, void* out_bf16, float* out_f32, float* out_lse,
+                   void* stream);
+
+/* a[i] = bf16(f32(a[i]) * sigmoid(f32(gate[i]))): mul_sigmoid_inplace,
+ * src/modeling/qwen3_5_moe/kernels.hpp:80-88. */
+int arc_mul_sigmoid_inplace(void* a, const void* gate, int64_t n, void* stream);
+
+/* Additive causal / sliding-window mask buffer: fill_causal_mask,
+ * src/common/kernels/attention_mask.hpp:12-38.  mask is (q_len, kv_len) f32. */
+int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,
+                         int32_t sliding_window, void* stream);
+
+/* Device-side status of the current device: 0, or the code of the first bounded
+ * wait that gave up since the last clear.  Synchronises the device. */
+int arc_sdpa_device_status(uint32_t* fault_code, uint32_t* fault_detail);
+int arc_sdpa_clear_device_status(void);
+
+/* Number of kernels this library has launched in this process (all devices). */
+uint64_t arc_sdpa_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARC_SDPA_H_ */
