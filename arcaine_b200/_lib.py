@@ -59,7 +59,7 @@ class DecodeParams(C.Structure):
         ("kv_len", C.c_void_p), ("kv_row_offset", C.c_void_p), ("out_f32", C.c_void_p), ("out_lse", C.c_void_p),
         ("batch", C.c_int32), ("nq", C.c_int32), ("nkv", C.c_int32), ("hd", C.c_int32),
         ("kv_len_uniform", C.c_int32), ("max_kv_len", C.c_int32),
-        ("q_stride_b", C.c_int64), ("o_stride_b", C.c_int64), ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64),
+        ("q_stride_b", C.c_int64), ("o_stride_b", C.c_int64), ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64), ("kv_rows_total", C.c_int64),
         ("scale", C.c_float), ("num_ctas", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
@@ -92,7 +92,7 @@ def load() -> C.CDLL:
     L.arc_sdpa_decode.restype = C.c_int
     L.arc_sdpa_decode.argtypes = [C.POINTER(DecodeParams), vp]
     L.arc_sdpa_merge.restype = C.c_int
-    L.arc_sdpa_merge.argtypes = [vp, vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, vp, vp, vp]
+    L.arc_sdpa_merge.argtypes = [vp, vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int64, vp, vp, vp, vp, vp]
     L.arc_mul_sigmoid_inplace.restype = C.c_int
     L.arc_mul_sigmoid_inplace.argtypes = [vp, vp, C.c_int64, vp]
     L.arc_fill_causal_mask.restype = C.c_int

@@ -120,6 +120,24 @@ static int make_tile_map(CUtensorMap* tm, const void* base, int hd, int heads, i
     return ARC_OK;
 }
 
+// (nkv*hd, rows) view of a KV cache whose rows are `stride_t` elements apart;
+// box = 64 columns x `box_rows` rows, 128-byte swizzle; rows past `rows` read as zero.
+static int make_cache_map(CUtensorMap* tm, const void* base, int row_elems, int64_t rows, int64_t stride_t,
+                          int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)row_elems, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)stride_t * 2u};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        std::snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled (cache) failed with CUresult %d", (int)r);
+        return ARC_ERR_CUDA;
+    }
+    return ARC_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Prefill plan
 // ---------------------------------------------------------------------------
@@ -206,6 +224,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         mp.out_lse = p->out_lse;
         mp.rows = plan.rows;
         mp.num_parts = plan.splits;
+        mp.o_part_stride = plan.rows * HD;
+        mp.lse_part_stride = plan.rows;
         mp.seq = p->seq;
         mp.nq = p->nq;
         mp.o_stride_b = p->o_stride_b;
@@ -234,6 +254,7 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
     if (p->hd != 128 && p->hd != 256) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
     if (!(p->scale > 0.f) || !std::isfinite(p->scale)) return ARC_ERR_BAD_SHAPE;
     if (!p->kv_len && p->kv_len_uniform < 0) return ARC_ERR_BAD_SHAPE;
+    if (p->kv_rows_total <= 0 || p->kv_rows_total > 0x7fffffffLL) return ARC_ERR_BAD_SHAPE;
     const int G = p->nq / p->nkv;
     if (G > 16) return ARC_ERR_UNSUPPORTED_GQA;
     plan->nt = G > 8 ? 2 : 1;
@@ -244,13 +265,13 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
         if (p->nkv % c == 0) nkv_cta = c;
     plan->nkv_cta = nkv_cta;
     plan->groups = p->nkv / nkv_cta;
-    const int pitch = nkv_cta * p->hd * 2 + 16;
-    int slices = (68 * 1024) / (32 * pitch);
+    const int row_bytes = nkv_cta * p->hd * 2;
+    int slices = (64 * 1024) / (32 * row_bytes);
     if (slices > 8 / nkv_cta) slices = 8 / nkv_cta;
     if (slices < 1) slices = 1;
     plan->slices = slices;
-    const int stage_bytes = 2 * 16 * slices * pitch;
-    const int fixed = 128 + 2 * 8 * 8 + (p->batch + 2) * 8;
+    const int stage_bytes = 2 * 16 * slices * row_bytes;
+    const int fixed = 1024 + 2 * 8 * 8 + (p->batch + 2) * 8;
     int stages = (smem_optin - kDecodeStaticSmem - fixed) / stage_bytes;
     if (stages > 4) stages = 4;
     if (stages < 2) return ARC_ERR_TOO_LARGE;
@@ -267,10 +288,12 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
 template <int HD>
 static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan, DeviceState* ds,
                          cudaStream_t stream) {
+    CUtensorMap tk, tv;
+    int rc;
+    if ((rc = make_cache_map(&tk, p->k, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
+    if ((rc = make_cache_map(&tv, p->v, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
     DecodeParams kp{};
     kp.q = static_cast<const uint16_t*>(p->q);
-    kp.k = static_cast<const uint16_t*>(p->k);
-    kp.v = static_cast<const uint16_t*>(p->v);
     kp.kv_len = p->kv_len;
     kp.kv_row_offset = reinterpret_cast<const long long*>(p->kv_row_offset);
     kp.part_o = static_cast<float*>(p->workspace);
@@ -292,9 +315,9 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     dim3 grid((unsigned)plan.ncta, (unsigned)plan.groups, 1);
     const unsigned threads = 32u * (unsigned)(plan.nkv_cta * plan.slices + 1);
     if (plan.nt == 1)
-        sdpa_decode_kernel<HD, 1><<<grid, threads, plan.smem_bytes, stream>>>(kp);
+        sdpa_decode_kernel<HD, 1><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
     else
-        sdpa_decode_kernel<HD, 2><<<grid, threads, plan.smem_bytes, stream>>>(kp);
+        sdpa_decode_kernel<HD, 2><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
 
@@ -410,8 +433,8 @@ extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
 }
 
 extern "C" int arc_sdpa_merge(const float* part_out, const float* part_lse, int32_t num_parts, int64_t rows,
-                              int32_t hd, const void* gate, void* out_bf16, float* out_f32, float* out_lse,
-                              void* stream) {
+                              int32_t hd, int64_t part_out_stride, int64_t part_lse_stride, const void* gate,
+                              void* out_bf16, float* out_f32, float* out_lse, void* stream) {
     if (!part_out || !part_lse) return ARC_ERR_NULL_POINTER;
     if (!out_bf16 && !out_f32) return ARC_ERR_NULL_POINTER;
     if (num_parts <= 0 || rows <= 0 || rows > 0x7fffffffLL) return ARC_ERR_BAD_SHAPE;
@@ -430,6 +453,9 @@ extern "C" int arc_sdpa_merge(const float* part_out, const float* part_lse, int3
     mp.rows = rows;
     mp.num_parts = num_parts;
     mp.seq = 0;
+    mp.o_part_stride = part_out_stride > 0 ? part_out_stride : rows * hd;
+    mp.lse_part_stride = part_lse_stride > 0 ? part_lse_stride : rows;
+    if ((mp.o_part_stride & 3) != 0) return ARC_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (hd == 128)
         sdpa_uniform_merge_kernel<128><<<(unsigned)rows, 64, 0, st>>>(mp);

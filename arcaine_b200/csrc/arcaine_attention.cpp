@@ -65,6 +65,7 @@ void run_decode(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v
     p.q_stride_b = p.o_stride_b = (int64_t)nq * hd;
     p.kv_stride_b = kv_len;
     p.kv_stride_t = (int64_t)nkv * hd;
+    p.kv_rows_total = kv_len;
     p.scale = scale;
     const size_t need = arc_sdpa_decode_workspace_bytes(&p);
     if (need == 0) throw_on(arc_sdpa_decode(&p, stream), where);  // reports the reason

@@ -7,10 +7,12 @@
 // per SM), so the load is balanced whatever the per-sequence lengths are and a
 // CTA streams one long contiguous run of cache rows.
 //
-// Inside a CTA a producer warp issues one 16-byte-aligned bulk async copy per
-// cache row (all KV heads of the CTA's head group: nkv_cta*hd*2 contiguous
-// bytes) into a ring of shared-memory stages; rows are padded by 16 bytes so
-// ldmatrix reads are bank-conflict free.  Consumer warps each own one KV head
+// Inside a CTA a producer warp streams the cache through a ring of
+// shared-memory stages with TMA: the K and V caches are described as 2-D tensors
+// (row = one position, all KV heads), and one copy moves a 64-element column
+// chunk of a whole stage of rows (16-64 rows, 2-8 KB) with the 128-byte swizzle,
+// so ldmatrix reads are bank-conflict free without padding and the copy engine
+// sees few, large requests.  Consumer warps each own one KV head
 // and a 16-key slice of every stage.  The GQA group of that head (<= 8 query
 // heads per n-tile) forms the N dimension of the warp MMAs, so K and V are read
 // from HBM and from shared memory exactly once per group:
@@ -26,6 +28,7 @@
 // split the key range (src/modeling/qwen3_5/kernels.hpp:761-905), or fold the
 // group into the MMA rows but launch only nkv*4 work-groups (:910-1054).
 #pragma once
+#include <cuda.h>
 #include <math_constants.h>
 
 #include "ptx.cuh"
@@ -36,8 +39,6 @@ constexpr int DECODE_MAX_BATCH = 2048;
 
 struct DecodeParams {
     const uint16_t* q;
-    const uint16_t* k;
-    const uint16_t* v;
     const int* kv_len;
     const long long* kv_row_offset;
     float* part_o;    // [(slot * slices + slice)][nq][HD]
@@ -79,15 +80,18 @@ __device__ __forceinline__ long long share_size(long long total, int ncta, int t
 }
 
 template <int HD, int NT>
-__global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(288, 1)
+    sdpa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int ncw = p.nkv_cta * p.slices;  // consumer warps
     const int tk = 16 * p.slices;          // keys per stage
     const int row_bytes = p.nkv_cta * HD * 2;
-    const int pitch = row_bytes + 16;
-    const int tile_bytes = tk * pitch;  // one of K / V
+    const int nchunks = p.nkv_cta * (HD / 64);  // 64-element column chunks per row
+    const int chunk_bytes = tk * 128;           // one chunk of one stage: tk rows x 128 bytes
+    const int tile_bytes = tk * row_bytes;      // one of K / V
     const int stage_bytes = 2 * tile_bytes;
 
     uint8_t* stage_base = smem;
@@ -110,12 +114,6 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
     const long long g0 = (long long)blockIdx.x * per;
     const long long g1 = min(total, g0 + per);
 
-    // Zero the staging ring so rows a short tile leaves unwritten hold finite data.
-    {
-        uint4* z = reinterpret_cast<uint4*>(stage_base);
-        const int n16 = p.stages * stage_bytes / 16;
-        for (int i = threadIdx.x; i < n16; i += blockDim.x) z[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
             mbar_init(&full[s], 1);
@@ -123,7 +121,6 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
         }
         fence_mbar_init();
     }
-    fence_proxy_async_smem();
     __syncthreads();
     if (g0 >= g1) return;
 
@@ -148,16 +145,17 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
                     ok = false;
                     break;
                 }
-                const int nk = min(tk, seg_keys - k0);
-                if (lane == 0) mbar_arrive_expect_tx(&full[st], (uint32_t)(2 * nk * row_bytes));
+                // A stage always carries tk full rows: rows past the segment end
+                // are masked by the consumers, rows past the cache end read as zero.
+                if (lane == 0) mbar_arrive_expect_tx(&full[st], (uint32_t)stage_bytes);
                 __syncwarp();
-                uint8_t* dstK = stage_base + (size_t)st * stage_bytes;
-                for (int r = lane; r < 2 * nk; r += 32) {
-                    const int is_v = r >= nk;
-                    const int key = r - is_v * nk;
-                    const uint16_t* src = (is_v ? p.v : p.k) + (row0 + k0 + key) * p.kv_stride_t + (long long)head0 * HD;
-                    bulk_load_1d(dstK + (size_t)is_v * tile_bytes + (size_t)key * pitch, src, (uint32_t)row_bytes,
-                                 &full[st]);
+                uint8_t* dst = stage_base + (size_t)st * stage_bytes;
+                const int row = (int)(row0 + k0);
+                for (int c = lane; c < 2 * nchunks; c += 32) {
+                    const int is_v = c >= nchunks;
+                    const int cc = c - is_v * nchunks;
+                    tma_load_2d(dst + (size_t)is_v * tile_bytes + (size_t)cc * chunk_bytes, is_v ? &tm_v : &tm_k,
+                                &full[st], head0 * HD + cc * 64, row);
                 }
             }
             g = seg_end;
@@ -220,10 +218,27 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
                 const int nk = min(tk, seg_keys - k0);
                 const int nvalid = min(16, nk - slice * 16);  // keys of this warp's slice
                 if (nvalid > 0) {
-                    const uint32_t sK = smem_u32(stage_base + (size_t)st * stage_bytes) + (slice * 16) * pitch + hl * HD * 2;
+                    // Swizzled addressing: 16-byte unit u of row r sits at unit u ^ (r & 7).
+                    const uint32_t sK = smem_u32(stage_base + (size_t)st * stage_bytes) + hl * (HD / 64) * chunk_bytes;
                     const uint32_t sV = sK + tile_bytes;
-                    const uint32_t a_k = sK + (lane & 15) * pitch + (lane >> 4) * 16;
-                    const uint32_t a_v = sV + ((lane & 7) + (lane >> 4) * 8) * pitch + ((lane >> 3) & 1) * 16;
+                    const int key_k = slice * 16 + (lane & 15);
+                    const int key_v = slice * 16 + (lane & 7) + (lane >> 4) * 8;
+                    const uint32_t a_k = sK + key_k * 128;
+                    const uint32_t a_v = sV + key_v * 128;
+                    const int xk = key_k & 7, hk = lane >> 4;
+                    const int xv = key_v & 7, hv = (lane >> 3) & 1;
+                    if (nvalid < 16) {
+                        // Rows past the segment end may hold anything (another sequence, or
+                        // never-written cache); clear this warp's V rows so 0 * x stays 0.
+                        for (int i = lane; i < (16 - nvalid) * (HD / 8); i += 32) {
+                            const int key = slice * 16 + nvalid + i / (HD / 8);
+                            const int u = i % (HD / 8);
+                            const uint32_t a = sV + (u >> 3) * chunk_bytes + key * 128 + (u & 7) * 16;
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(a), "r"(0u) : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                    }
 
                     float acc[NT][2][4];
 #pragma unroll
@@ -233,7 +248,7 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         uint32_t a[4];
-                        ldmatrix_x4(a, a_k + kk * 32);
+                        ldmatrix_x4(a, a_k + (kk >> 2) * chunk_bytes + ((((kk & 3) * 2 + hk) ^ xk) << 4));
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(acc[nt][kk & 1], a, qf[nt][kk][0], qf[nt][kk][1]);
                     }
@@ -282,7 +297,7 @@ __global__ void __launch_bounds__(288, 1) sdpa_decode_kernel(const DecodeParams 
 #pragma unroll
                     for (int mt = 0; mt < HD / 16; ++mt) {
                         uint32_t a[4];
-                        ldmatrix_x4_trans(a, a_v + mt * 32);
+                        ldmatrix_x4_trans(a, a_v + (mt >> 2) * chunk_bytes + ((((mt & 3) * 2 + hv) ^ xv) << 4));
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(o[nt][mt], a, pb[nt][0], pb[nt][1]);
                     }
@@ -401,7 +416,8 @@ __global__ void __launch_bounds__(HD / 2) sdpa_decode_merge_kernel(const DecodeM
 
 // ---------------------------------------------------------------------------
 // Merge of `num_parts` uniformly strided partial sets: part_o (parts, rows, hd),
-// part_lse (parts, rows).  One block per row.  Used for split prefill tiles and
+// part_lse (parts, rows), consecutive parts o_part_stride / lse_part_stride
+// elements apart (so one packed record per part works too).  One block per row.  Used for split prefill tiles and
 // for records gathered from other GPUs.  out rows are contiguous (rows, hd)
 // unless row_tokens > 0, in which case row = (b, t, h) is scattered with the
 // given strides (prefill output layout).
@@ -414,6 +430,7 @@ struct UniformMergeParams {
     float* out_f32;
     float* out_lse;
     long long rows;
+    long long o_part_stride, lse_part_stride;  // elements between consecutive parts
     int num_parts;
     int seq, nq;  // seq > 0: strided (b, t, h) addressing of out / gate
     long long o_stride_b, o_stride_t;
@@ -424,16 +441,16 @@ __global__ void __launch_bounds__(HD / 2) sdpa_uniform_merge_kernel(const Unifor
     const long long row = blockIdx.x;
     const int d = threadIdx.x * 2;
     float mx = -CUDART_INF_F;
-    for (int i = 0; i < p.num_parts; ++i) mx = fmaxf(mx, p.part_lse[(long long)i * p.rows + row]);
+    for (int i = 0; i < p.num_parts; ++i) mx = fmaxf(mx, p.part_lse[(long long)i * p.lse_part_stride + row]);
     float acc0 = 0.f, acc1 = 0.f, lse = -CUDART_INF_F;
     if (mx > -CUDART_INF_F) {
         float z = 0.f;
         for (int i = 0; i < p.num_parts; ++i) {
-            const float li = p.part_lse[(long long)i * p.rows + row];
+            const float li = p.part_lse[(long long)i * p.lse_part_stride + row];
             if (li == -CUDART_INF_F) continue;
             const float w = __expf(li - mx);
             z += w;
-            const float2 ov = *reinterpret_cast<const float2*>(p.part_o + ((long long)i * p.rows + row) * HD + d);
+            const float2 ov = *reinterpret_cast<const float2*>(p.part_o + (long long)i * p.o_part_stride + row * HD + d);
             acc0 = fmaf(w, ov.x, acc0);
             acc1 = fmaf(w, ov.y, acc1);
         }

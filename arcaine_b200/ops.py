@@ -132,6 +132,7 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
                 kv_len: Union[int, torch.Tensor, None] = None, kv_row_offset: Optional[torch.Tensor] = None,
                 gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, want_out: bool = True, num_ctas: int = 0,
+                partial_out: Optional[torch.Tensor] = None, partial_lse: Optional[torch.Tensor] = None,
                 workspace: Optional[Workspace] = None):
     """Split-KV decode of one query token per sequence.
 
@@ -160,6 +161,7 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
             raise ValueError("k/v: unsupported strides")
         p.kv_stride_t = k.stride(1)
         p.kv_stride_b = k.stride(0) // k.stride(1)
+        p.kv_rows_total = (B - 1) * p.kv_stride_b + max_len
     elif k.dim() == 3:
         rows, nkv, hdk = k.shape
         if v.shape != k.shape or k.stride(2) != 1 or k.stride(1) != hdk or k.stride() != v.stride():
@@ -167,6 +169,7 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
         max_len = rows
         p.kv_stride_t = k.stride(0)
         p.kv_stride_b = 0
+        p.kv_rows_total = rows
         if kv_row_offset is None and B > 1:
             raise ValueError("packed caches need kv_row_offset")
     else:
@@ -204,8 +207,13 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
         p.gate = gate.data_ptr()
     out_f32 = lse = None
     if return_partial:
-        out_f32 = torch.empty((B, nq, hd), dtype=torch.float32, device=q.device)
-        lse = torch.empty((B, nq), dtype=torch.float32, device=q.device)
+        out_f32 = partial_out if partial_out is not None else torch.empty((B, nq, hd), dtype=torch.float32, device=q.device)
+        lse = partial_lse if partial_lse is not None else torch.empty((B, nq), dtype=torch.float32, device=q.device)
+        _require(out_f32, torch.float32, "partial_out")
+        _require(lse, torch.float32, "partial_lse")
+        if tuple(out_f32.shape) != (B, nq, hd) or tuple(lse.shape) != (B, nq) or not out_f32.is_contiguous() \
+                or not lse.is_contiguous():
+            raise ValueError("partial_out / partial_lse must be contiguous (B, nq, hd) / (B, nq) f32")
         p.out_f32, p.out_lse = out_f32.data_ptr(), lse.data_ptr()
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.batch, p.nq, p.nkv, p.hd = B, nq, nkv, hd
@@ -223,11 +231,13 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
 
 def sdpa_merge(part_out: torch.Tensor, part_lse: torch.Tensor, *, gate: Optional[torch.Tensor] = None,
                out: Optional[torch.Tensor] = None, want_f32: bool = False, want_lse: bool = False):
-    """LSE merge of partial results: part_out (P, rows..., hd) f32, part_lse (P, rows...) f32."""
+    """LSE merge of partial results: part_out (P, rows..., hd) f32, part_lse (P, rows...) f32.
+
+    The leading (part) dimension may be strided — e.g. views into one packed
+    ``[out | lse]`` record per rank — as long as each part is dense.
+    """
     _require(part_out, torch.float32, "part_out")
     _require(part_lse, torch.float32, "part_lse")
-    if not part_out.is_contiguous() or not part_lse.is_contiguous():
-        raise ValueError("partials must be contiguous")
     P, hd = part_out.shape[0], part_out.shape[-1]
     row_shape = tuple(part_out.shape[1:-1])
     rows = 1
@@ -235,6 +245,10 @@ def sdpa_merge(part_out: torch.Tensor, part_lse: torch.Tensor, *, gate: Optional
         rows *= s
     if tuple(part_lse.shape) != (P, *row_shape):
         raise ValueError("part_lse shape mismatch")
+    if not part_out[0].is_contiguous() or not part_lse[0].is_contiguous():
+        raise ValueError("each part must be dense")
+    so = part_out.stride(0) if P > 1 else rows * hd
+    sl = part_lse.stride(0) if P > 1 else rows
     if out is None:
         out = torch.empty((*row_shape, hd), dtype=torch.bfloat16, device=part_out.device)
     _require(out, torch.bfloat16, "out")
@@ -247,7 +261,7 @@ def sdpa_merge(part_out: torch.Tensor, part_lse: torch.Tensor, *, gate: Optional
     o32 = torch.empty((*row_shape, hd), dtype=torch.float32, device=part_out.device) if want_f32 else None
     lse = torch.empty(row_shape, dtype=torch.float32, device=part_out.device) if want_lse else None
     with torch.cuda.device(part_out.device):
-        check(_lib.load().arc_sdpa_merge(part_out.data_ptr(), part_lse.data_ptr(), P, rows, hd,
+        check(_lib.load().arc_sdpa_merge(part_out.data_ptr(), part_lse.data_ptr(), P, rows, hd, so, sl,
                                          gate.data_ptr() if gate is not None else None, out.data_ptr(),
                                          o32.data_ptr() if o32 is not None else None,
                                          lse.data_ptr() if lse is not None else None, _stream_ptr(part_out)),

@@ -1,0 +1,157 @@
+"""Multi-GPU partitioning of the attention path: one process per GPU, torch.distributed plumbing.
+
+Two partitions, both without any collective inside the kernels:
+
+* prefill / canvas — KV heads (with their query-head groups) and, once the heads
+  run out, whole sequences are dealt to ranks; each rank computes its slice of the
+  output.  The only exchange is an optional all-gather of the output slices.
+* long-context decode — the KV *sequence* is cut into one contiguous slice per
+  rank, the single-token queries are replicated.  Every rank produces one packed
+  record ``[out f32 (B, nq, hd) | lse f32 (B, nq)]``; one all-gather moves the
+  records and every rank folds them with the log-sum-exp merge kernel, which also
+  applies the optional sigmoid gate.
+
+The reference has neither (its two GPUs split layers and copy activations through
+host memory, src/modeling/diffusion_gemma/model.cpp:33-46), so there is no
+reference call to mirror; the record layout and merge identity are this
+library's own.  The planning and exchange functions below are plain host logic on
+torch tensors and run unchanged on CPU tensors over ``gloo``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------------------
+# Partition planning (pure host logic)
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class HeadShard:
+    """Slice of a (batch, tokens, heads, hd) problem owned by one rank."""
+    kv_head_begin: int
+    kv_head_end: int
+    q_head_begin: int
+    q_head_end: int
+    batch_begin: int
+    batch_end: int
+
+    @property
+    def empty(self) -> bool:
+        return self.kv_head_begin >= self.kv_head_end or self.batch_begin >= self.batch_end
+
+
+def plan_head_shards(nq: int, nkv: int, batch: int, world: int) -> list[HeadShard]:
+    """Deal KV heads first, then sequences, to ``world`` ranks.
+
+    ``world`` is factored as head_ways x batch_ways with head_ways the largest
+    divisor of ``world`` that also divides ``nkv``; batch_ways must then divide
+    into ``batch`` (ranks beyond the available work get an empty shard).
+    """
+    if nq % nkv != 0:
+        raise ValueError("nq must be a multiple of nkv")
+    group = nq // nkv
+    head_ways = 1
+    for d in range(1, world + 1):
+        if world % d == 0 and nkv % d == 0:
+            head_ways = d
+    batch_ways = world // head_ways
+    heads_per = nkv // head_ways
+    shards = []
+    for r in range(world):
+        hw, bw = r % head_ways, r // head_ways
+        b0 = min(batch, (batch * bw + batch_ways - 1) // batch_ways)
+        b1 = min(batch, (batch * (bw + 1) + batch_ways - 1) // batch_ways)
+        k0, k1 = hw * heads_per, (hw + 1) * heads_per
+        shards.append(HeadShard(k0, k1, k0 * group, k1 * group, b0, b1))
+    return shards
+
+
+def plan_seq_shards(kv_len: int, world: int, align: int = 64) -> list[tuple[int, int]]:
+    """Contiguous [begin, end) key ranges, one per rank, boundaries aligned to ``align`` keys."""
+    per = -(-kv_len // world)
+    per = -(-per // align) * align
+    return [(min(kv_len, r * per), min(kv_len, (r + 1) * per)) for r in range(world)]
+
+
+# ---------------------------------------------------------------------------
+# Record exchange (works on CPU tensors over gloo and CUDA tensors over NCCL)
+# ---------------------------------------------------------------------------
+def record_numel(batch: int, nq: int, hd: int) -> int:
+    """Floats in one packed record, padded to a multiple of 4 so every part stays 16-byte aligned."""
+    n = batch * nq * hd + batch * nq
+    return (n + 3) // 4 * 4
+
+
+def split_record(record: torch.Tensor, batch: int, nq: int, hd: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Views (out (..., B, nq, hd), lse (..., B, nq)) into packed record(s); the last dim is the record."""
+    n_out, n_lse = batch * nq * hd, batch * nq
+    out = record[..., :n_out].unflatten(-1, (batch, nq, hd))
+    lse = record[..., n_out:n_out + n_lse].unflatten(-1, (batch, nq))
+    return out, lse
+
+
+def exchange_records(record: torch.Tensor, gathered: Optional[torch.Tensor] = None,
+                     group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather one packed record per rank into a (world, numel) tensor."""
+    world = dist.get_world_size(group)
+    if gathered is None:
+        gathered = torch.empty((world, record.numel()), dtype=record.dtype, device=record.device)
+    if world == 1:
+        gathered[0].copy_(record)
+        return gathered
+    dist.all_gather_into_tensor(gathered.view(-1), record.contiguous().view(-1), group=group)
+    return gathered
+
+
+# ---------------------------------------------------------------------------
+# GPU entry points
+# ---------------------------------------------------------------------------
+class SeqShardedDecode:
+    """Sequence-sharded decode step with persistent exchange buffers.
+
+    Each rank holds keys [begin, end) of every sequence (``k_local``/``v_local``:
+    (B, local_len, nkv, hd)) and the full query.  ``__call__`` enqueues, on the
+    current stream: local split-KV decode writing straight into the send record,
+    one all-gather, one merge.
+    """
+
+    def __init__(self, batch: int, nq: int, hd: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        from . import ops  # GPU-only import
+        self._ops = ops
+        self.batch, self.nq, self.hd = batch, nq, hd
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        n = record_numel(batch, nq, hd)
+        self.record = torch.empty(n, dtype=torch.float32, device=device)
+        self.gathered = torch.empty((self.world, n), dtype=torch.float32, device=device)
+        self.part_out, self.part_lse = split_record(self.record, batch, nq, hd)
+        self.all_out, self.all_lse = split_record(self.gathered, batch, nq, hd)
+        self.out = torch.empty((batch, nq, hd), dtype=torch.bfloat16, device=device)
+
+    def __call__(self, q, k_local, v_local, *, scale, kv_len=None, gate=None):
+        ops = self._ops
+        ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, return_partial=True, want_out=False,
+                        partial_out=self.part_out, partial_lse=self.part_lse)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
+            return ops.sdpa_merge(self.all_out, self.all_lse, gate=gate, out=self.out)
+        return ops.sdpa_merge(self.part_out.unsqueeze(0), self.part_lse.unsqueeze(0), gate=gate, out=self.out)
+
+
+def prefill_head_sharded(q_local, k_local, v_local, *, scale, mask_type, window, gate_local=None, out_local=None,
+                         gather_into: Optional[torch.Tensor] = None, group: Optional[dist.ProcessGroup] = None):
+    """Prefill on this rank's head/batch shard; optionally all-gather the output slices.
+
+    ``gather_into``: (world, *out_local.shape) bf16 buffer; when given, every
+    rank ends up with all slices (slice r = what rank r computed).
+    """
+    from . import ops
+    out_local = ops.sdpa_prefill(q_local, k_local, v_local, scale=scale, mask_type=mask_type, window=window,
+                                 gate=gate_local, out=out_local)
+    if gather_into is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_gather_into_tensor(gather_into.view(-1), out_local.contiguous().view(-1), group=group)
+    return out_local

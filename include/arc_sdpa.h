@@ -128,6 +128,8 @@ typedef struct arc_sdpa_decode_params {
     int64_t q_stride_b, o_stride_b; /* elements */
     int64_t kv_stride_b;            /* rows between sequences (when kv_row_offset == NULL) */
     int64_t kv_stride_t;            /* elements between consecutive rows (>= nkv*hd) */
+    int64_t kv_rows_total;          /* rows addressable from k and v (extent of the cache
+                                       buffers); loads never reach beyond it */
     float scale;
     int32_t num_ctas; /* 0 -> one per SM */
     void* workspace;
@@ -141,13 +143,16 @@ int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream);
  * Log-sum-exp merge of `num_parts` partial results over disjoint key ranges
  * (no counterpart in the reference, which never splits the key range):
  *   lse = log sum_c exp(lse_c),  out = sum_c exp(lse_c - lse) * o_c.
- * part_out (num_parts, rows, hd) f32, part_lse (num_parts, rows) f32.
+ * part_out (num_parts, rows, hd) f32, part_lse (num_parts, rows) f32; part c
+ * starts part_out_stride / part_lse_stride ELEMENTS after part c-1 (0 = dense:
+ * rows*hd and rows), so a packed per-rank record [out | lse] can be merged in
+ * place after an all-gather.
  * Outputs (each optional): out_bf16 (rows, hd) with the optional sigmoid gate
  * (rows, hd) bf16 applied, out_f32 (rows, hd) ungated, out_lse (rows).
  * ------------------------------------------------------------------------- */
 int arc_sdpa_merge(const float* part_out, const float* part_lse, int32_t num_parts, int64_t rows,
-                   int32_t hd, const void* gate, void* out_bf16, float* out_f32, float* out_lse,
-                   void* stream);
+                   int32_t hd, int64_t part_out_stride, int64_t part_lse_stride, const void* gate,
+                   void* out_bf16, float* out_f32, float* out_lse, void* stream);
 
 /* a[i] = bf16(f32(a[i]) * sigmoid(f32(gate[i]))): mul_sigmoid_inplace,
  * src/modeling/qwen3_5_moe/kernels.hpp:80-88. */

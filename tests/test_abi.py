@@ -1,0 +1,75 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/*.h declares."""
+import ctypes
+import glob
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    names = []
+    for path in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"typedef struct.*?\}\s*\w+;", "", text, flags=re.S)
+        names += re.findall(r"\b(arc_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for must in ("arc_sdpa_prefill", "arc_sdpa_decode", "arc_sdpa_merge", "arc_sdpa_prefill_workspace_bytes",
+                 "arc_sdpa_decode_workspace_bytes", "arc_mul_sigmoid_inplace", "arc_fill_causal_mask"):
+        assert must in names
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from arcaine_b200 import _lib
+    lib = _lib.load()
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    for name in _lib.EXPORTS:
+        assert name in declared_functions(), f"{name} bound in Python but not declared in include/"
+    assert lib.arc_sdpa_status_string(0) == b"ok"
+    assert b"128 or 256" in lib.arc_sdpa_status_string(_lib.ARC_ERR_UNSUPPORTED_HEAD_DIM)
+
+
+def test_struct_layouts_match_the_header():
+    """ctypes mirrors of the parameter structs have the field order of the C declarations."""
+    from arcaine_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "arc_sdpa.h")).read()
+    for cname, cls in (("arc_sdpa_prefill_params", _lib.PrefillParams), ("arc_sdpa_decode_params", _lib.DecodeParams)):
+        body = re.search(r"typedef struct " + cname + r" \{(.*?)\} " + cname + ";", text, flags=re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            names = decl.replace("*", " ").split(",")
+            first = names[0].split()[-1]
+            fields.append(first)
+            fields += [n.strip() for n in names[1:]]
+        assert fields == [f[0] for f in cls._fields_], cname
+
+
+def test_no_cpu_fallback():
+    """The operators refuse CPU tensors instead of computing somewhere else."""
+    from arcaine_b200 import ops
+    q = torch.zeros(4, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.sdpa_prefill(q, q, q, scale=1.0)
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.sdpa_decode(q, q, q, scale=1.0)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from arcaine_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libarc_sdpa.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()

@@ -1,0 +1,162 @@
+"""Parity of the sm_100a prefill / canvas kernel with the CPU oracle, through the C ABI."""
+import ctypes as C
+
+import pytest
+import torch
+
+from helpers import assert_close, seeded_bf16
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from arcaine_b200 import ops as o
+    o.clear_device_status()
+    yield o
+    assert o.device_status() == (0, 0), "a bounded device-side wait gave up during the prefill tests"
+
+
+def run_case(ops, seq, kv_len, nq, nkv, hd, scale, mask_type, window, seed, num_splits=0, gate=False, lse=False):
+    q, k, v = seeded_bf16(seq, nq, hd, seed=seed), seeded_bf16(kv_len, nkv, hd, seed=seed + 1), \
+        seeded_bf16(kv_len, nkv, hd, seed=seed + 2)
+    g = seeded_bf16(seq, nq, hd, seed=seed + 3) if gate else None
+    res = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=scale, mask_type=mask_type, window=window,
+                           num_splits=num_splits, gate=g.cuda() if gate else None, return_lse=lse)
+    want = oracle.sdpa_f32(q, k, v, scale=scale, mask_type=mask_type, window=window, gate=g, want_lse=lse)
+    if lse:
+        assert_close(res[0], want[0], "out")
+        finite = torch.isfinite(want[2])
+        assert torch.equal(torch.isfinite(res[1].cpu()), finite)
+        assert torch.allclose(res[1].cpu()[finite], want[2][finite], atol=2e-3)
+    else:
+        assert_close(res, want[0], f"S{seq} L{kv_len} nq{nq}/{nkv} hd{hd} mask{mask_type} w{window}")
+
+
+@pytest.mark.parametrize("hd", [128, 256])
+@pytest.mark.parametrize("mask_type,window", [(0, oracle.INT_MAX), (3, oracle.INT_MAX), (3, 100), (3, 1)])
+def test_single_sequence(ops, hd, mask_type, window):
+    run_case(ops, 300, 300, 8, 4, hd, hd ** -0.5, mask_type, window, seed=100 + hd)
+
+
+@pytest.mark.parametrize("seq,kv_len", [(1, 1), (1, 129), (77, 300), (128, 128), (129, 127), (130, 1000), (200, 517)])
+@pytest.mark.parametrize("mask_type,window", [(0, oracle.INT_MAX), (3, oracle.INT_MAX), (3, 64)])
+def test_ragged_shapes(ops, seq, kv_len, mask_type, window):
+    # includes kv_len < seq with bottom-right causal: leading queries see no key and must be zero
+    run_case(ops, seq, kv_len, 4, 2, 128, 0.09, mask_type, window, seed=seq * 7 + kv_len, lse=True)
+
+
+def test_config1_cpu_runnable_case(ops):
+    """B1, 8Q/4KV, hd128, seq 512, non-causal, scale 1/sqrt(128)."""
+    run_case(ops, 512, 512, 8, 4, 128, 128 ** -0.5, 0, oracle.INT_MAX, seed=1)
+
+
+@pytest.mark.parametrize("scale", [1.0, 256 ** -0.5])
+def test_config2_canvas_over_prompt_steps(ops, scale):
+    """DiffusionGemma denoising steps: 2048 cached prompt rows + a 256-row canvas written at the cache
+    tail each step (src/modeling/diffusion_gemma/attention.cpp:1079-1103); 3 of the 32 steps here,
+    scale 1.0 is what the reference runs, 1/sqrt(256) the conditioned variant."""
+    nq, nkv, hd, prompt, canvas = 16, 8, 256, 2048, 256
+    kc = torch.empty(prompt + canvas, nkv, hd, dtype=torch.bfloat16)
+    vc = torch.empty_like(kc)
+    kc[:prompt], vc[:prompt] = seeded_bf16(prompt, nkv, hd, seed=2000), seeded_bf16(prompt, nkv, hd, seed=2001)
+    kd, vd = kc.cuda(), vc.cuda()
+    for step in (0, 1, 31):
+        q = seeded_bf16(canvas, nq, hd, seed=2100 + step)
+        kc[prompt:], vc[prompt:] = seeded_bf16(canvas, nkv, hd, seed=2200 + step), seeded_bf16(canvas, nkv, hd, seed=2300 + step)
+        kd[prompt:].copy_(kc[prompt:])
+        vd[prompt:].copy_(vc[prompt:])
+        got = ops.gqa_attention_sdpa(q.cuda(), canvas, nq, hd, kd, vd, prompt + canvas, nkv) if scale == 1.0 else \
+            ops.sdpa_prefill(q.cuda(), kd, vd, scale=scale)
+        rows = list(range(0, canvas * nq, 5))
+        want, _ = oracle.sdpa_f32(q, kc, vc, scale=scale, rows=rows)
+        assert_close(got.reshape(-1, hd)[rows], want, f"step {step}")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 0])
+def test_key_range_splits_agree(ops, splits):
+    run_case(ops, 256, 1100, 4, 2, 256, 0.0625, 3, 700, seed=31, num_splits=splits, lse=True)
+
+
+def test_gate_epilogue_and_split_gate(ops):
+    run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True)
+    run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True, num_splits=2)
+
+
+def test_explicit_mask_equals_inline_rule(ops):
+    seq, kv_len, nq, nkv, hd = 140, 260, 4, 2, 128
+    q, k, v = seeded_bf16(seq, nq, hd, seed=51).cuda(), seeded_bf16(kv_len, nkv, hd, seed=52).cuda(), \
+        seeded_bf16(kv_len, nkv, hd, seed=53).cuda()
+    mask = ops.fill_causal_mask(seq, kv_len, past_offset=kv_len - seq, sliding_window=50)
+    assert torch.equal(mask.cpu(), torch.from_numpy(oracle.fill_causal_mask(seq, kv_len, kv_len - seq, 50)))
+    a = ops.sdpa_prefill(q, k, v, scale=0.1, mask_type=ops.MASK_EXPLICIT, mask=mask)
+    b = ops.sdpa_prefill(q, k, v, scale=0.1, mask_type=ops.MASK_CAUSAL, window=50)
+    assert_close(a, b.float(), "explicit vs inline", rel_tol=2e-3, abs_tol=4e-3)
+
+
+def test_batched_strided_inputs_and_output_aliasing_query(ops):
+    """batch 3 inside a larger cache allocation (token and batch strides), out written over q."""
+    B, S, L, cap, nq, nkv, hd = 3, 140, 200, 256, 8, 4, 128
+    q = seeded_bf16(B, S, nq, hd, seed=61)
+    kc = seeded_bf16(B, cap, nkv, hd, seed=62)
+    vc = seeded_bf16(B, cap, nkv, hd, seed=63)
+    qd = q.cuda()
+    out = ops.sdpa_prefill(qd, kc.cuda()[:, :L], vc.cuda()[:, :L], scale=0.09, mask_type=3, out=qd)
+    assert out.data_ptr() == qd.data_ptr()
+    for b in range(B):
+        want, _ = oracle.sdpa_f32(q[b], kc[b, :L], vc[b, :L], scale=0.09, mask_type=3)
+        assert_close(out[b], want, f"batch {b}")
+
+
+def test_reference_named_entry_points(ops):
+    seq, past, nq, nkv, hd = 130, 70, 8, 2, 256
+    q, k, v = seeded_bf16(seq, nq, hd, seed=71), seeded_bf16(past + seq, nkv, hd, seed=72), seeded_bf16(past + seq, nkv, hd, seed=73)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    # qwen35_xmx_attention: causal over past + seq keys, output aliasing the query buffer
+    buf = qd.clone()
+    ops.qwen35_xmx_attention(buf, kd, vd, buf, seq, past, nq, nkv, hd, 0.0625)
+    assert_close(buf, oracle.qwen35_online_attention(q, k, v, seq=seq, past=past, scale=0.0625).float(), "qwen35")
+    # gqa_attention: no scale; inputs scaled down so the softmax is not one-hot
+    qs = (q.float() * 0.25).bfloat16()
+    got = ops.gqa_attention(qs.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, past, 64, True)
+    want, _ = oracle.sdpa_f32(qs, k, v, scale=1.0, mask_type=3, window=64)
+    assert_close(got, want, "gqa_attention")
+    assert_close(got, oracle.gqa_attention(qs, k, v, past_offset=past, sliding_window=64, causal=True).float(),
+                 "gqa_attention vs its restatement")
+    got = ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX, scale=0.0625)
+    assert_close(got, oracle.batched_attention(q, k, v, past_offset=past, scale=0.0625).float(), "batched_attention")
+    with pytest.raises(RuntimeError):
+        ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX, block_ids=torch.zeros(1))
+
+
+def test_error_statuses(ops):
+    from arcaine_b200 import _lib
+    q = torch.zeros(8, 4, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.ArcError) as e:
+        ops.sdpa_prefill(q, q, q, scale=1.0)
+    assert e.value.status == _lib.ARC_ERR_UNSUPPORTED_HEAD_DIM
+    q = torch.zeros(8, 6, 128, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(8, 4, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.ArcError) as e:
+        ops.sdpa_prefill(q, k, k, scale=1.0)
+    assert e.value.status == _lib.ARC_ERR_BAD_SHAPE
+    q = torch.zeros(8, 4, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.ArcError) as e:
+        ops.sdpa_prefill(q, k, k, scale=-1.0)
+    assert e.value.status == _lib.ARC_ERR_BAD_SHAPE
+    # raw ABI: misaligned pointer, missing workspace for a forced split
+    p = _lib.PrefillParams()
+    big = torch.zeros(600, 4, 128, dtype=torch.bfloat16, device="cuda")
+    p.q = p.k = p.v = p.out = big.data_ptr()
+    p.batch, p.seq, p.kv_len, p.nq, p.nkv, p.hd = 1, 600, 600, 4, 4, 128
+    for f in ("q", "k", "v", "o"):
+        setattr(p, f + "_stride_t", 512)
+        setattr(p, f + "_stride_b", 600 * 512)
+    p.scale, p.mask_type, p.window, p.num_splits = 1.0, 0, ops.NO_WINDOW, 2
+    L = _lib.load()
+    assert L.arc_sdpa_prefill(C.byref(p), None) == _lib.ARC_ERR_WORKSPACE_TOO_SMALL
+    p.num_splits = 1
+    p.q = big.data_ptr() + 2
+    assert L.arc_sdpa_prefill(C.byref(p), None) == _lib.ARC_ERR_ALIGNMENT
+    assert L.arc_sdpa_prefill(None, None) == _lib.ARC_ERR_NULL_POINTER
