@@ -287,13 +287,6 @@ ORACLE_API int oracle_gqa_attention(const uint16_t* Q, int seq, int nq, int hd,
             for (int64_t r = 0; r < total; ++r) {
                 int t = (int)(r / nq), h = (int)(r % nq), kh = h / g;
                 const uint16_t* qrow = Q + ((size_t)t * nq + h) * hd;
-                for (int j = 0; j < kv_len; ++j) {
-                    const uint16_t* krow = Kc + ((size_t)j * nkv + kh) * hd;
-                    float dot = 0.0f;
-#pragma omp simd reduction(+ : dot)
-                    for (int d = 0; d < hd; ++d) dot += b2f(qrow[d]) * b2f(krow[d]);
-                    x[j] = f2b(dot);
-                }
                 int q_global = past_offset + t;
                 int lo = 0, hi = kv_len;
                 if (causal) {
@@ -304,15 +297,21 @@ ORACLE_API int oracle_gqa_attention(const uint16_t* Q, int seq, int nq, int hd,
                         lo = l > 0 ? l : 0;
                     }
                 }
+                /* Scores only inside the visible band (the reference slices the
+                 * same band per query tile, attention.cpp:721-769). */
+                for (int j = lo; j < hi; ++j) {
+                    const uint16_t* krow = Kc + ((size_t)j * nkv + kh) * hd;
+                    float dot = 0.0f;
+#pragma omp simd reduction(+ : dot)
+                    for (int d = 0; d < hd; ++d) dot += b2f(qrow[d]) * b2f(krow[d]);
+                    x[j] = f2b(dot);
+                }
                 float m = -3.4028235e38f;
                 for (int c = lo; c < hi; ++c) m = fmaxf(m, b2f(x[c]));
                 float z = 0.0f;
                 for (int c = lo; c < hi; ++c) z += expf(b2f(x[c]) - m);
                 float inv_z = 1.0f / z;
-                for (int c = 0; c < kv_len; ++c) {
-                    float p = (c >= lo && c < hi) ? expf(b2f(x[c]) - m) * inv_z : 0.0f;
-                    x[c] = f2b(p);
-                }
+                for (int c = lo; c < hi; ++c) x[c] = f2b(expf(b2f(x[c]) - m) * inv_z);
                 for (int d = 0; d < hd; ++d) acc[d] = 0.0f;
                 for (int c = lo; c < hi; ++c) {
                     float p = b2f(x[c]);

@@ -122,10 +122,14 @@ def test_reference_named_entry_points(ops):
     got = ops.gqa_attention(qs.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, past, 64, True)
     want, _ = oracle.sdpa_f32(qs, k, v, scale=1.0, mask_type=3, window=64)
     assert_close(got, want, "gqa_attention")
+    # the restated matmul path keeps scores and probabilities in bf16, so it is itself
+    # ~5e-2 away from the fp32 oracle at these magnitudes; this is a sanity bound, not the gate
     assert_close(got, oracle.gqa_attention(qs, k, v, past_offset=past, sliding_window=64, causal=True).float(),
-                 "gqa_attention vs its restatement")
+                 "gqa_attention vs its restatement", rel_tol=2e-2, abs_tol=1.5e-1)
     got = ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX, scale=0.0625)
-    assert_close(got, oracle.batched_attention(q, k, v, past_offset=past, scale=0.0625).float(), "batched_attention")
+    assert_close(got, oracle.batched_attention(q, k, v, past_offset=past, scale=0.0625).float(), "batched_attention",
+                 rel_tol=2e-2, abs_tol=1.5e-1)
+    assert_close(got, oracle.sdpa_f32(q, k, v, scale=0.0625, mask_type=3)[0], "batched_attention vs fp32 oracle")
     with pytest.raises(RuntimeError):
         ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX, block_ids=torch.zeros(1))
 
