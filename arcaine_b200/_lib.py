@@ -30,10 +30,11 @@ MASK_NONE = 0
 MASK_EXPLICIT = 1
 MASK_CAUSAL = 3
 NO_WINDOW = 2**31 - 1
+STATIC_SCRATCH_BYTES = 8 << 20
 
 EXPORTS = (
     "arc_sdpa_status_string", "arc_sdpa_last_error", "arc_sdpa_prefill_workspace_bytes", "arc_sdpa_prefill",
-    "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
+    "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
     "arc_fill_causal_mask", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
 )
 
@@ -91,6 +92,8 @@ def load() -> C.CDLL:
     L.arc_sdpa_decode_workspace_bytes.argtypes = [C.POINTER(DecodeParams)]
     L.arc_sdpa_decode.restype = C.c_int
     L.arc_sdpa_decode.argtypes = [C.POINTER(DecodeParams), vp]
+    L.arc_sdpa_decode_static.restype = C.c_int
+    L.arc_sdpa_decode_static.argtypes = [C.POINTER(DecodeParams), vp]
     L.arc_sdpa_merge.restype = C.c_int
     L.arc_sdpa_merge.argtypes = [vp, vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, C.c_int64, vp, vp, vp, vp, vp]
     L.arc_mul_sigmoid_inplace.restype = C.c_int

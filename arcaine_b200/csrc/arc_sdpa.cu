@@ -432,6 +432,60 @@ extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
     return p->hd == 128 ? launch_decode<128>(p, plan, ds, st) : launch_decode<256>(p, plan, ds, st);
 }
 
+// ---------------------------------------------------------------------------
+// Decode without any caller-provided or allocated scratch.
+//
+// Some callers have nowhere to get a workspace from: a serving process whose
+// memory planner has already handed every free byte of the GPU to its own arena
+// (Arcaine's per-GPU arena works that way), or a thin foreign-function caller
+// that owns no device allocator at all; and cudaMalloc on a decode loop would
+// also stall the whole device.  For them the split-KV partial records live in
+// the fixed array below, which is part of the library image: every GPU that
+// loads the library carries these 8 MiB until the process exits.
+//
+// In host code the array's name is only a handle; the device address is looked
+// up once per device (with that device current) and that address is what the
+// kernels receive.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[ARC_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[arc::kMaxDevices];
+
+static int static_scratch_address(void** out) {
+    int dev = 0;
+    ARC_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= arc::kMaxDevices) return ARC_ERR_CUDA;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        std::lock_guard<std::mutex> lock(arc::g_mu);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            void* ptr = nullptr;
+            ARC_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+            g_static_scratch_addr[dev] = ptr;
+        }
+    }
+    *out = g_static_scratch_addr[dev];
+    return ARC_OK;
+}
+
+extern "C" int arc_sdpa_decode_static(const arc_sdpa_decode_params* p, void* stream) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != ARC_OK) return rc;
+    arc_sdpa_decode_params q = *p;
+    q.workspace = nullptr;
+    q.workspace_bytes = 0;
+    const size_t need = arc_sdpa_decode_workspace_bytes(&q);
+    if (need > (size_t)ARC_STATIC_SCRATCH_BYTES) {
+        std::snprintf(g_last_error, sizeof(g_last_error),
+                      "arc_sdpa_decode_static: this shape needs %zu bytes of scratch, the built-in array holds %zu",
+                      need, (size_t)ARC_STATIC_SCRATCH_BYTES);
+        return ARC_ERR_TOO_LARGE;
+    }
+    q.workspace = scratch;
+    q.workspace_bytes = ARC_STATIC_SCRATCH_BYTES;
+    return arc_sdpa_decode(&q, stream);
+}
+
 extern "C" int arc_sdpa_merge(const float* part_out, const float* part_lse, int32_t num_parts, int64_t rows,
                               int32_t hd, int64_t part_out_stride, int64_t part_lse_stride, const void* gate,
                               void* out_bf16, float* out_f32, float* out_lse, void* stream) {

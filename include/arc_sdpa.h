@@ -140,6 +140,32 @@ size_t arc_sdpa_decode_workspace_bytes(const arc_sdpa_decode_params* p);
 int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream);
 
 /* -------------------------------------------------------------------------
+ * arc_sdpa_decode without a workspace.  No counterpart in the reference: it
+ * exists for callers that cannot obtain device scratch themselves — a server
+ * whose planner has already given all GPU memory to its own arena, or a thin
+ * foreign-language binding with no device allocator — and for loops where a
+ * cudaMalloc (which stalls the device) is not acceptable.
+ *
+ * Same parameters and results as arc_sdpa_decode; `workspace` and
+ * `workspace_bytes` are ignored.  The partial records go to an array of
+ * ARC_STATIC_SCRATCH_BYTES built into the library image (each GPU that loads
+ * the library holds it until the process exits).  The call allocates nothing:
+ * no cudaMalloc / cudaFree, no allocating library routine.
+ *   - Shapes whose arc_sdpa_decode_workspace_bytes() exceeds
+ *     ARC_STATIC_SCRATCH_BYTES are refused with ARC_ERR_TOO_LARGE
+ *     (arc_sdpa_last_error() gives both sizes).
+ *   - The first call on each device resolves the array's device address; make
+ *     that first call before starting any stream capture on that device.
+ *   - All calls on a device share the one array, which keeps whatever the last
+ *     call left in it.  Nothing needs clearing between calls — a call writes
+ *     every record it later reads — but two calls that overlap on the GPU
+ *     (different streams, no ordering between them) race on it: keep them on one
+ *     stream or order them with events.
+ * ------------------------------------------------------------------------- */
+#define ARC_STATIC_SCRATCH_BYTES (8u << 20)
+int arc_sdpa_decode_static(const arc_sdpa_decode_params* p, void* stream);
+
+/* -------------------------------------------------------------------------
  * Log-sum-exp merge of `num_parts` partial results over disjoint key ranges
  * (no counterpart in the reference, which never splits the key range):
  *   lse = log sum_c exp(lse_c),  out = sum_c exp(lse_c - lse) * o_c.
