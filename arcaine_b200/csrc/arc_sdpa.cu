@@ -279,6 +279,7 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
     plan->smem_bytes = stages * stage_bytes + fixed;
     int ncta = p->num_ctas > 0 ? p->num_ctas : sm_count / plan->groups;
     if (ncta < 1) ncta = 1;
+    if (ncta > 1024) ncta = 1024;
     plan->ncta = ncta;
     plan->parts = ((long long)ncta + p->batch) * slices;
     plan->ws_bytes = (size_t)plan->parts * p->nq * ((size_t)p->hd + 1) * sizeof(float);
@@ -336,7 +337,9 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     mp.slices = plan.slices;
     mp.o_stride_b = p->o_stride_b;
     dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
-    sdpa_decode_merge_kernel<HD><<<mgrid, HD / 2, (size_t)(p->batch + 2) * 8, stream>>>(mp);
+    const size_t merge_smem = (size_t)(p->batch + 2) * 8 + 8 * sizeof(float) + (size_t)(MERGE_THREADS / 32) * HD * sizeof(float) +
+                              (size_t)(plan.ncta + 1) * plan.slices * sizeof(float);  // a sequence spans at most ncta shares
+    sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, merge_smem, stream>>>(mp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
     return ARC_OK;

@@ -366,51 +366,107 @@ __device__ __forceinline__ float sigmoid_gate(float attn, uint16_t gate_bits) {
     return bf16_round(attn) * (1.0f / (1.0f + __expf(-g)));
 }
 
+constexpr int MERGE_THREADS = 256;
+
+// Block-wide max / sum over MERGE_THREADS threads (result to every thread).
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, t) : v + t;
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = scratch[0];
+#pragma unroll
+    for (int w = 1; w < MERGE_THREADS / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+    return r;
+}
+
 template <int HD>
-__global__ void __launch_bounds__(HD / 2) sdpa_decode_merge_kernel(const DecodeMergeParams p) {
+__global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const DecodeMergeParams p) {
     extern __shared__ uint8_t smem_raw[];
     long long* cum = reinterpret_cast<long long*>(smem_raw);
+    float* red = reinterpret_cast<float*>(cum + p.batch + 2);      // 8 floats
+    float* acc_sm = red + 8;                                        // (warps) x HD
+    float* wgt = acc_sm + (MERGE_THREADS / 32) * HD;                // one weight per record
     build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
     const int h = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total = cum[p.batch];
     const long long per = share_size(total, p.ncta, 16 * p.slices);
     const long long k_begin = cum[b], k_end = cum[b + 1];
-    const int d = threadIdx.x * 2;
-    float acc0 = 0.f, acc1 = 0.f, lse = -CUDART_INF_F;
-    if (k_end > k_begin) {
+    constexpr int VPL = HD / 32;  // output values per lane
+    float acc[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
+    float lse = -CUDART_INF_F, inv = 0.f;
+    if (k_end > k_begin) {  // block-uniform
         const int c_first = (int)(k_begin / per), c_last = (int)((k_end - 1) / per);
         const int n_parts = (c_last - c_first + 1) * p.slices;
         const long long part0 = ((long long)c_first + b) * p.slices;
+        // weights: every thread takes a strided set of records
         float mx = -CUDART_INF_F;
-        for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, p.part_lse[(part0 + i) * p.nq + h]);
+        for (int i = threadIdx.x; i < n_parts; i += MERGE_THREADS) {
+            const float li = p.part_lse[(part0 + i) * p.nq + h];
+            wgt[i] = li;
+            mx = fmaxf(mx, li);
+        }
+        mx = block_reduce(mx, true, red);
         float z = 0.f;
         if (mx > -CUDART_INF_F) {
-            for (int i = 0; i < n_parts; ++i) {
-                const float li = p.part_lse[(part0 + i) * p.nq + h];
-                if (li == -CUDART_INF_F) continue;
-                const float w = __expf(li - mx);
+            for (int i = threadIdx.x; i < n_parts; i += MERGE_THREADS) {
+                const float w = __expf(wgt[i] - mx);  // exp(-inf) = 0 for empty records
+                wgt[i] = w;
                 z += w;
-                const float2 ov = *reinterpret_cast<const float2*>(p.part_o + ((part0 + i) * p.nq + h) * HD + d);
-                acc0 = fmaf(w, ov.x, acc0);
-                acc1 = fmaf(w, ov.y, acc1);
             }
-            const float inv = 1.f / z;
-            acc0 *= inv;
-            acc1 *= inv;
+        }
+        z = block_reduce(z, false, red);  // also orders the wgt[] writes before the reads below
+        if (z > 0.f) {
+            inv = 1.f / z;
             lse = mx + __logf(z);
+            // each warp folds every 8th record; a lane owns VPL consecutive output values
+            for (int i = warp; i < n_parts; i += MERGE_THREADS / 32) {
+                const float w = wgt[i];
+                if (w == 0.f) continue;
+                const float* src = p.part_o + ((part0 + i) * p.nq + h) * HD + lane * VPL;
+#pragma unroll
+                for (int j = 0; j < VPL; j += 4) {
+                    const float4 ov = *reinterpret_cast<const float4*>(src + j);
+                    acc[j] = fmaf(w, ov.x, acc[j]);
+                    acc[j + 1] = fmaf(w, ov.y, acc[j + 1]);
+                    acc[j + 2] = fmaf(w, ov.z, acc[j + 2]);
+                    acc[j + 3] = fmaf(w, ov.w, acc[j + 3]);
+                }
+            }
         }
     }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) acc_sm[warp * HD + lane * VPL + j] = acc[j];
+    __syncthreads();
     const long long row = (long long)b * p.nq + h;
-    if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(acc0, acc1);
     if (p.out_lse && threadIdx.x == 0) p.out_lse[row] = lse;
-    if (p.out) {
-        const long long eoff = (long long)b * p.o_stride_b + (long long)h * HD + d;
-        if (p.gate) {
-            const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff);
-            acc0 = sigmoid_gate(acc0, (uint16_t)(gw & 0xffffu));
-            acc1 = sigmoid_gate(acc1, (uint16_t)(gw >> 16));
+    if (threadIdx.x < HD / 2) {
+        const int d = threadIdx.x * 2;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < MERGE_THREADS / 32; ++w) {
+            a0 += acc_sm[w * HD + d];
+            a1 += acc_sm[w * HD + d + 1];
         }
-        *reinterpret_cast<uint32_t*>(p.out + eoff) = pack_bf16x2(acc0, acc1);
+        a0 *= inv;
+        a1 *= inv;
+        if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(a0, a1);
+        if (p.out) {
+            const long long eoff = (long long)b * p.o_stride_b + (long long)h * HD + d;
+            if (p.gate) {
+                const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff);
+                a0 = sigmoid_gate(a0, (uint16_t)(gw & 0xffffu));
+                a1 = sigmoid_gate(a1, (uint16_t)(gw >> 16));
+            }
+            *reinterpret_cast<uint32_t*>(p.out + eoff) = pack_bf16x2(a0, a1);
+        }
     }
 }
 

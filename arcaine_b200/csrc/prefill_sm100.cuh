@@ -59,6 +59,114 @@ struct PrefillCfg {
     static constexpr int MIN_CTAS = (HD == 128) ? 2 : 1;
 };
 
+// Per-row visibility for blocks that need element masking.
+struct RowMask {
+    int lo, hi;            // visible keys [lo, hi)
+    int kv_len;
+    const float* mask_row;  // optional additive mask row (natural-log domain)
+};
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Element masking mode of a key block: 0 = every key visible, 1 = per-row span
+// [lo, hi), 2 = span plus an additive f32 mask row.
+// Scaled (log2-domain) and masked score of one key.
+template <int MODE>
+__device__ __forceinline__ float masked_score(uint32_t raw, float sl, int key, const RowMask& rm) {
+    float x = __uint_as_float(raw) * sl;
+    if (MODE == 2) {
+        if (rm.mask_row && key < rm.kv_len) x += rm.mask_row[key] * 1.4426950408889634f;
+    }
+    return (key >= rm.lo && key < rm.hi) ? x : -CUDART_INF_F;
+}
+
+// Maximum of one 32-column chunk, folded into four independent running maxima.
+template <int MODE>
+__device__ __forceinline__ void chunk_max(const uint32_t (&v)[32], float (&mx)[4], float sl, int key0,
+                                          const RowMask& rm) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float a, b;
+            if (MODE != 0) {
+                a = masked_score<MODE>(v[e + 2 * u], sl, key0 + e + 2 * u, rm);
+                b = masked_score<MODE>(v[e + 2 * u + 1], sl, key0 + e + 2 * u + 1, rm);
+            } else {
+                a = __uint_as_float(v[e + 2 * u]);
+                b = __uint_as_float(v[e + 2 * u + 1]);
+            }
+            mx[u] = max3f(mx[u], a, b);
+        }
+    }
+}
+
+// exp2 of one chunk against the running max, packed to bf16x2; four independent partial sums.
+template <int MODE>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk)[16], float (&ls)[4], float sl,
+                                          float m_eff, int key0, const RowMask& rm) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        float p0, p1;
+        if (MODE != 0) {
+            p0 = fast_exp2(masked_score<MODE>(v[e], sl, key0 + e, rm) - m_eff);
+            p1 = fast_exp2(masked_score<MODE>(v[e + 1], sl, key0 + e + 1, rm) - m_eff);
+        } else {
+            p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, -m_eff));
+            p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
+        }
+        ls[(e >> 1) & 3] += p0 + p1;
+        pk[e >> 1] = pack_bf16x2(p0, p1);
+    }
+}
+
+// Pass 1 over the 128 score columns of this thread's row: block maximum (raw scores for
+// MODE 0, scaled + masked otherwise).  The chunk loop is kept rolled (two chunks per trip,
+// one loading while the other is reduced) so the kernel stays small in the instruction cache.
+// Leaves chunk 0 loading into `va` for pass 2.
+template <int MODE>
+__device__ __forceinline__ float row_block_max(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
+                                               int key0, const RowMask& rm) {
+    float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    tmem_ld32(tS, va);
+#pragma unroll 1
+    for (int cc = 0; cc < 128; cc += 64) {
+        tmem_wait_ld();
+        tmem_ld32(tS + cc + 32, vb);
+        chunk_max<MODE>(va, mx4, sl, key0 + cc, rm);
+        tmem_wait_ld();
+        tmem_ld32(tS + ((cc + 64) & 127), va);
+        chunk_max<MODE>(vb, mx4, sl, key0 + cc + 32, rm);
+    }
+    return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+
+// Pass 2: probabilities as bf16 over the S columns (chunk c lands in columns [16c, 16c+16),
+// all of which have been read by then); returns the row sum of the unrounded probabilities.
+// Expects chunk 0 already loading into `va`.
+template <int MODE>
+__device__ __forceinline__ float row_block_exp(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
+                                               float m_eff, int key0, const RowMask& rm) {
+    float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t pk[16];
+#pragma unroll 1
+    for (int cc = 0; cc < 128; cc += 64) {
+        tmem_wait_ld();
+        tmem_ld32(tS + cc + 32, vb);
+        chunk_exp<MODE>(va, pk, ls4, sl, m_eff, key0 + cc, rm);
+        tmem_st16(tS + (cc >> 1), pk);
+        tmem_wait_ld();
+        if (cc == 0) tmem_ld32(tS + 64, va);
+        chunk_exp<MODE>(vb, pk, ls4, sl, m_eff, key0 + cc + 32, rm);
+        tmem_st16(tS + (cc >> 1) + 16, pk);
+    }
+    return (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+}
+
 template <int HD>
 __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_CTAS)
     sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -236,7 +344,6 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
         const uint32_t tS = tmem_base + lane_sel + C::COL_S;
         const uint32_t tO = tmem_base + lane_sel + C::COL_O;
         const float sl = p.scale_log2;
-        constexpr float LOG2E = 1.4426950408889634f;
 
         int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
         if (causal) {
@@ -256,7 +363,8 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
         float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
         float l = 0.f;
         bool ok = true;
-        uint32_t v[32];
+        uint32_t va[32], vb[32];  // two chunk buffers: one is processed while the other loads
+        const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
 
         for (int i = 0; i < n_my; ++i) {
             const int key0 = (my_lo + i) * C::BN;
@@ -268,26 +376,11 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             tc_fence_after_sync();
             const bool edge = has_mask || (key0 + C::BN > tile_hi_min) || (key0 < tile_lo_max);
 
-            // Pass 1: block maximum of this row.
-            float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(tS + c * 32, v);
-                tmem_wait_ld();
-                if (!edge) {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int key = key0 + c * 32 + e;
-                        float x = __uint_as_float(v[e]) * sl;
-                        if (mask_row && key < p.kv_len) x += mask_row[key] * LOG2E;
-                        x = (key >= row_lo && key < row_hi) ? x : -CUDART_INF_F;
-                        mx = fmaxf(mx, x);
-                    }
-                }
-            }
+            const int mode = has_mask ? 2 : (edge ? 1 : 0);
+            float mx;
+            if (mode == 0) mx = row_block_max<0>(tS, va, vb, sl, key0, rm);
+            else if (mode == 1) mx = row_block_max<1>(tS, va, vb, sl, key0, rm);
+            else mx = row_block_max<2>(tS, va, vb, sl, key0, rm);
             const float m_blk = edge ? mx : mx * sl;
             const float m_new = fmaxf(m, m_blk);
             if (i == 0) {
@@ -295,14 +388,16 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             } else {
                 const bool need = m_new > m + 8.0f;
                 if (__any_sync(0xffffffffu, need)) {
+                    // Rare: the row maximum grew by more than 2^8; rescale O in tensor memory.
                     const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                    tmem_wait_ld();
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; ++c) {
-                        tmem_ld32(tO + c * 32, v);
+                        tmem_ld32(tO + c * 32, vb);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                        tmem_st32(tO + c * 32, v);
+                        for (int e = 0; e < 32; ++e) vb[e] = __float_as_uint(__uint_as_float(vb[e]) * alpha);
+                        tmem_st32(tO + c * 32, vb);
                     }
                     l *= alpha;
                     m = m_new;
@@ -310,40 +405,9 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             }
             const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
 
-            // Pass 2: probabilities -> bf16 into the S columns, row sum in fp32.
-            float lsum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(tS + c * 32, v);
-                tmem_wait_ld();
-                uint32_t pk[16];
-                if (!edge) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, -m_eff));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
-                        lsum += p0 + p1;
-                        pk[e >> 1] = pack_bf16x2(p0, p1);
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        float pp[2];
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            const int key = key0 + c * 32 + e + u;
-                            float x = __uint_as_float(v[e + u]) * sl;
-                            if (mask_row && key < p.kv_len) x += mask_row[key] * LOG2E;
-                            x = (key >= row_lo && key < row_hi) ? x : -CUDART_INF_F;
-                            pp[u] = fast_exp2(x - m_eff);
-                        }
-                        lsum += pp[0] + pp[1];
-                        pk[e >> 1] = pack_bf16x2(pp[0], pp[1]);
-                    }
-                }
-                tmem_st16(tS + c * 16, pk);
-            }
-            l += lsum;
+            if (mode == 0) l += row_block_exp<0>(tS, va, vb, sl, m_eff, key0, rm);
+            else if (mode == 1) l += row_block_exp<1>(tS, va, vb, sl, m_eff, key0, rm);
+            else l += row_block_exp<2>(tS, va, vb, sl, m_eff, key0, rm);
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_full);
@@ -363,14 +427,14 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                 float* dst = p.part_o + ((long long)split * rows_total + row) * HD;
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
-                    tmem_ld32(tO + c * 32, v);
+                    tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
                         for (int e = 0; e < 32; e += 4)
                             *reinterpret_cast<float4*>(dst + c * 32 + e) =
-                                make_float4(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv,
-                                            __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+                                make_float4(__uint_as_float(va[e]) * inv, __uint_as_float(va[e + 1]) * inv,
+                                            __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
                     }
                 }
                 if (store) p.part_lse[(long long)split * rows_total + row] = lse;
@@ -380,14 +444,14 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                 const uint16_t* g = p.gate ? p.gate + eoff : nullptr;
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
-                    tmem_ld32(tO + c * 32, v);
+                    tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
                     if (store) {
 #pragma unroll
                         for (int e = 0; e < 32; e += 8) {
                             float o[8];
 #pragma unroll
-                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(v[e + u]) * inv;
+                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(va[e + u]) * inv;
                             if (g) {
                                 const uint4 gv = *reinterpret_cast<const uint4*>(g + c * 32 + e);
                                 const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
