@@ -208,6 +208,10 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.mask_type = p->mask_type;
     kp.window = p->window;
     kp.num_splits = plan.splits;
+#ifdef ARC_PREFILL_TRACE
+    kp.trace = reinterpret_cast<long long*>(p->out_lse);  // debug builds reuse the lse slot as the trace buffer
+    kp.out_lse = nullptr;
+#endif
 
     dim3 grid((unsigned)plan.q_tiles, (unsigned)p->nq, (unsigned)(p->batch * plan.splits));
     sdpa_prefill_kernel<HD><<<grid, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);

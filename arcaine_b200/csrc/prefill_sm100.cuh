@@ -41,6 +41,9 @@ struct PrefillParams {
     float scale_log2;  // scale * log2(e)
     int mask_type, window;
     int num_splits;
+#ifdef ARC_PREFILL_TRACE
+    long long* trace;  // debug builds only: per-block timestamps of CTA 0
+#endif
 };
 
 template <int HD>
@@ -124,31 +127,69 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk
     }
 }
 
-// Pass 1 over the 128 score columns of this thread's row: block maximum (raw scores for
-// MODE 0, scaled + masked otherwise).  The chunk loop is kept rolled (two chunks per trip,
-// one loading while the other is reduced) so the kernel stays small in the instruction cache.
+// How a 32-key chunk relates to the rows of this warp (warp-uniform, so the
+// warp-collective TMEM instructions stay converged): 0 = every key visible to all
+// 32 rows (no element test needed), 1 = mixed, 2 = no key visible to any row.
+// With a causal diagonal crossing a 128 x 128 block, each warp meets at most one
+// or two mixed chunks; the rest is either plain or skipped.
+__device__ __forceinline__ int chunk_class(int kc, const RowMask& rm) {
+    const bool all = rm.lo <= kc && kc + 32 <= rm.hi;
+    const bool none = rm.hi <= kc || rm.lo >= kc + 32;
+    if (__all_sync(0xffffffffu, all)) return 0;
+    if (__all_sync(0xffffffffu, none)) return 2;
+    return 1;
+}
+
+template <bool ADD_MASK>
+__device__ __forceinline__ void chunk_max_any(const uint32_t (&v)[32], float (&mx_raw)[4], float (&mx_scaled)[4],
+                                              float sl, int kc, const RowMask& rm) {
+    const int cls = ADD_MASK ? 1 : chunk_class(kc, rm);
+    if (cls == 0) chunk_max<0>(v, mx_raw, sl, kc, rm);
+    else if (cls == 1) chunk_max<ADD_MASK ? 2 : 1>(v, mx_scaled, sl, kc, rm);
+}
+
+template <bool ADD_MASK>
+__device__ __forceinline__ void chunk_exp_any(const uint32_t (&v)[32], uint32_t (&pk)[16], float (&ls)[4], float sl,
+                                              float m_eff, int kc, const RowMask& rm) {
+    const int cls = ADD_MASK ? 1 : chunk_class(kc, rm);
+    if (cls == 0) {
+        chunk_exp<0>(v, pk, ls, sl, m_eff, kc, rm);
+    } else if (cls == 1) {
+        chunk_exp<ADD_MASK ? 2 : 1>(v, pk, ls, sl, m_eff, kc, rm);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) pk[e] = 0u;
+    }
+}
+
+// Pass 1 over the 128 score columns of this thread's row: block maximum in the scaled
+// (log2) domain.  The chunk loop is kept rolled (two chunks per trip, one loading while
+// the other is reduced) so the kernel stays small in the instruction cache.
 // Leaves chunk 0 loading into `va` for pass 2.
-template <int MODE>
+template <bool ADD_MASK>
 __device__ __forceinline__ float row_block_max(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
                                                int key0, const RowMask& rm) {
-    float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
     tmem_ld32(tS, va);
 #pragma unroll 1
     for (int cc = 0; cc < 128; cc += 64) {
         tmem_wait_ld();
         tmem_ld32(tS + cc + 32, vb);
-        chunk_max<MODE>(va, mx4, sl, key0 + cc, rm);
+        chunk_max_any<ADD_MASK>(va, mr, ms, sl, key0 + cc, rm);
         tmem_wait_ld();
         tmem_ld32(tS + ((cc + 64) & 127), va);
-        chunk_max<MODE>(vb, mx4, sl, key0 + cc + 32, rm);
+        chunk_max_any<ADD_MASK>(vb, mr, ms, sl, key0 + cc + 32, rm);
     }
-    return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    const float raw = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
+    const float scaled = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
+    return fmaxf(raw * sl, scaled);
 }
 
 // Pass 2: probabilities as bf16 over the S columns (chunk c lands in columns [16c, 16c+16),
 // all of which have been read by then); returns the row sum of the unrounded probabilities.
 // Expects chunk 0 already loading into `va`.
-template <int MODE>
+template <bool ADD_MASK>
 __device__ __forceinline__ float row_block_exp(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
                                                float m_eff, int key0, const RowMask& rm) {
     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -157,11 +198,11 @@ __device__ __forceinline__ float row_block_exp(uint32_t tS, uint32_t (&va)[32], 
     for (int cc = 0; cc < 128; cc += 64) {
         tmem_wait_ld();
         tmem_ld32(tS + cc + 32, vb);
-        chunk_exp<MODE>(va, pk, ls4, sl, m_eff, key0 + cc, rm);
+        chunk_exp_any<ADD_MASK>(va, pk, ls4, sl, m_eff, key0 + cc, rm);
         tmem_st16(tS + (cc >> 1), pk);
         tmem_wait_ld();
         if (cc == 0) tmem_ld32(tS + 64, va);
-        chunk_exp<MODE>(vb, pk, ls4, sl, m_eff, key0 + cc + 32, rm);
+        chunk_exp_any<ADD_MASK>(vb, pk, ls4, sl, m_eff, key0 + cc + 32, rm);
         tmem_st16(tS + (cc >> 1) + 16, pk);
     }
     return (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
@@ -315,10 +356,16 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                 }
                 umma_commit(k_empty);
                 umma_commit(s_full);
+#ifdef ARC_PREFILL_TRACE
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && i < 16) p.trace[i * 8 + 7] = clock64();
+#endif
                 if (!mbar_wait(p_full, i & 1)) {
                     report_fault(p.fault, FAULT_WAIT_P, i);
                     break;
                 }
+#ifdef ARC_PREFILL_TRACE
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && i < 16) p.trace[i * 8 + 5] = clock64();
+#endif
                 if (!mbar_wait(v_full, i & 1)) {
                     report_fault(p.fault, FAULT_WAIT_V, i);
                     break;
@@ -333,6 +380,9 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                             (i > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(v_empty);
+#ifdef ARC_PREFILL_TRACE
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && i < 16) p.trace[i * 8 + 6] = clock64();
+#endif
             }
             umma_commit(o_full);
         }
@@ -352,11 +402,6 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             if (windowed) row_lo = max(0, diag - p.window + 1);
             if (row_lo > row_hi) row_lo = row_hi;
         }
-        int tile_hi_min = p.kv_len, tile_lo_max = 0;
-        if (causal) {
-            tile_hi_min = min(max(q0 + off + 1, 0), p.kv_len);
-            if (windowed) tile_lo_max = max(0, q_last + off - p.window + 1);
-        }
         const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
         const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
 
@@ -368,20 +413,24 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
 
         for (int i = 0; i < n_my; ++i) {
             const int key0 = (my_lo + i) * C::BN;
+#ifdef ARC_PREFILL_TRACE
+            const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
+            if (tr) p.trace[i * 8 + 0] = clock64();
+#endif
             if (!mbar_wait_warp(s_full, i & 1)) {
                 report_fault(p.fault, FAULT_WAIT_S, i);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            const bool edge = has_mask || (key0 + C::BN > tile_hi_min) || (key0 < tile_lo_max);
-
-            const int mode = has_mask ? 2 : (edge ? 1 : 0);
-            float mx;
-            if (mode == 0) mx = row_block_max<0>(tS, va, vb, sl, key0, rm);
-            else if (mode == 1) mx = row_block_max<1>(tS, va, vb, sl, key0, rm);
-            else mx = row_block_max<2>(tS, va, vb, sl, key0, rm);
-            const float m_blk = edge ? mx : mx * sl;
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 8 + 1] = clock64();
+#endif
+            const float m_blk = has_mask ? row_block_max<true>(tS, va, vb, sl, key0, rm)
+                                         : row_block_max<false>(tS, va, vb, sl, key0, rm);
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 8 + 2] = clock64();
+#endif
             const float m_new = fmaxf(m, m_blk);
             if (i == 0) {
                 m = m_new;
@@ -405,12 +454,17 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             }
             const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
 
-            if (mode == 0) l += row_block_exp<0>(tS, va, vb, sl, m_eff, key0, rm);
-            else if (mode == 1) l += row_block_exp<1>(tS, va, vb, sl, m_eff, key0, rm);
-            else l += row_block_exp<2>(tS, va, vb, sl, m_eff, key0, rm);
+            l += has_mask ? row_block_exp<true>(tS, va, vb, sl, m_eff, key0, rm)
+                          : row_block_exp<false>(tS, va, vb, sl, m_eff, key0, rm);
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 8 + 3] = clock64();
+#endif
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(p_full);
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 8 + 4] = clock64();
+#endif
         }
 
         if (ok && !mbar_wait_warp(o_full, 0)) {
