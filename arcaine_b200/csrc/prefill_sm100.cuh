@@ -56,10 +56,15 @@ struct PrefillCfg {
     static constexpr int TMEM_COLS = (HD == 128) ? 256 : 512;
     static constexpr int COL_S = 0;    // 128 fp32 columns; P (bf16) aliases the first 64
     static constexpr int COL_O = 128;  // HD fp32 columns
-    static constexpr int NUM_BARS = 8;
-    static constexpr int SMEM_BYTES = 3 * TILE_BYTES + NUM_BARS * 8 + 16 + 1024;
-    static constexpr int THREADS = 192;
+    static constexpr int NUM_BARS = 9;
+    static constexpr int XCH_BYTES = (2 * 2 * 128 + 2 * 128) * 4;  // row-max exchange (2 phases) + row-sum exchange
+    static constexpr int SMEM_BYTES = 3 * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_BYTES + 1024;
+    static constexpr int THREADS = 384;  // 3 warpgroups: softmax A, softmax B, {TMA, MMA, 2 idle warps}
     static constexpr int MIN_CTAS = (HD == 128) ? 2 : 1;
+    // Register re-split between warpgroups (hd128, two CTAs per SM: 80 registers per thread at launch).
+    static constexpr bool RESPLIT = (HD == 128);
+    static constexpr int REGS_SOFTMAX = 104;
+    static constexpr int REGS_OTHER = 24;
 };
 
 // Per-row visibility for blocks that need element masking.
@@ -162,50 +167,21 @@ __device__ __forceinline__ void chunk_exp_any(const uint32_t (&v)[32], uint32_t 
     }
 }
 
-// Pass 1 over the 128 score columns of this thread's row: block maximum in the scaled
-// (log2) domain.  The chunk loop is kept rolled (two chunks per trip, one loading while
-// the other is reduced) so the kernel stays small in the instruction cache.
-// Leaves chunk 0 loading into `va` for pass 2.
-template <bool ADD_MASK>
-__device__ __forceinline__ float row_block_max(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
-                                               int key0, const RowMask& rm) {
-    float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-    float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-    tmem_ld32(tS, va);
-#pragma unroll 1
-    for (int cc = 0; cc < 128; cc += 64) {
-        tmem_wait_ld();
-        tmem_ld32(tS + cc + 32, vb);
-        chunk_max_any<ADD_MASK>(va, mr, ms, sl, key0 + cc, rm);
-        tmem_wait_ld();
-        tmem_ld32(tS + ((cc + 64) & 127), va);
-        chunk_max_any<ADD_MASK>(vb, mr, ms, sl, key0 + cc + 32, rm);
-    }
-    const float raw = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
-    const float scaled = fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3]));
-    return fmaxf(raw * sl, scaled);
+
+// Barrier between the two warps that share a set of 32 query rows (warp w and w + 4):
+// hardware barrier 1 + w, 64 threads.  Every softmax warp executes exactly one pair_sync per
+// key block and one after the loop, whatever happened to its waits, so neither can hang here.
+__device__ __forceinline__ void pair_sync(int pair) {
+    asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
 }
 
-// Pass 2: probabilities as bf16 over the S columns (chunk c lands in columns [16c, 16c+16),
-// all of which have been read by then); returns the row sum of the unrounded probabilities.
-// Expects chunk 0 already loading into `va`.
-template <bool ADD_MASK>
-__device__ __forceinline__ float row_block_exp(uint32_t tS, uint32_t (&va)[32], uint32_t (&vb)[32], float sl,
-                                               float m_eff, int key0, const RowMask& rm) {
-    float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t pk[16];
-#pragma unroll 1
-    for (int cc = 0; cc < 128; cc += 64) {
-        tmem_wait_ld();
-        tmem_ld32(tS + cc + 32, vb);
-        chunk_exp_any<ADD_MASK>(va, pk, ls4, sl, m_eff, key0 + cc, rm);
-        tmem_st16(tS + (cc >> 1), pk);
-        tmem_wait_ld();
-        if (cc == 0) tmem_ld32(tS + 64, va);
-        chunk_exp_any<ADD_MASK>(vb, pk, ls4, sl, m_eff, key0 + cc + 32, rm);
-        tmem_st16(tS + (cc >> 1) + 16, pk);
-    }
-    return (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+template <int R>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(R));
+}
+template <int R>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(R));
 }
 
 template <int HD>
@@ -229,6 +205,8 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
     uint64_t* o_full = bars + 7;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
+    float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][half 2][row 128]
+    float* xch_sum = xch_max + 2 * 2 * 128;                    // [half 2][row 128]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -289,11 +267,11 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
         mbar_init(v_full, 1);
         mbar_init(v_empty, 1);
         mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        mbar_init(p_full, 256);
         mbar_init(o_full, 1);
         fence_mbar_init();
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
     }
@@ -302,9 +280,10 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp == 4) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+    if (warp >= 8) {
+        if (C::RESPLIT) setmaxnreg_dec<C::REGS_OTHER>();
+        if (warp == 8 && lane == 0) {
+            // -------------------------------------------------------------- TMA producer
             prefetch_tensormap(&tm_q);
             prefetch_tensormap(&tm_k);
             prefetch_tensormap(&tm_v);
@@ -330,10 +309,8 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                 for (int c = 0; c < C::CH; ++c)
                     tma_load_4d(sV + c * C::CHUNK_BYTES, &tm_v, v_full, c * 64, kvh, key0, b);
             }
-        }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        } else if (warp == 9 && lane == 0) {
+            // -------------------------------------------------------------- MMA issuer
             constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
             const uint32_t tS = tmem_base + C::COL_S;
@@ -371,12 +348,15 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                     break;
                 }
                 tc_fence_after_sync();
-                // O += P V : P from tensor memory (8 columns per 16 keys), V
-                // MN-major: 64-element head-dim chunks 16 KB apart (leading
-                // offset), 8-key groups 1024 bytes apart (stride offset).
+                // O += P V : P from tensor memory, 8 columns per 16 keys; the two key
+                // halves of a block keep their P at the start of their own S columns
+                // (keys 0-63 at columns 0-31, keys 64-127 at columns 64-95).  V is
+                // MN-major: 64-element head-dim chunks 16 KB apart (leading offset),
+                // 8-key groups 1024 bytes apart (stride offset).
 #pragma unroll
                 for (int ks = 0; ks < C::BN / 16; ++ks) {
-                    umma_ts(tO, tS + ks * 8, make_smem_desc_sw128(aV + ks * 2048, C::CHUNK_BYTES, 1024), IDESC_PV,
+                    const uint32_t pcol = (ks < 4) ? ks * 8 : 64 + (ks - 4) * 8;
+                    umma_ts(tO, tS + pcol, make_smem_desc_sw128(aV + ks * 2048, C::CHUNK_BYTES, 1024), IDESC_PV,
                             (i > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(v_empty);
@@ -388,11 +368,16 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
         }
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
-        const int r = threadIdx.x;
+        // Two threads per query row: warps 0-3 own keys 0-63 of every block (S columns
+        // 0-63), warps 4-7 keys 64-127; both halves of a row sit in the same TMEM lane.
+        if (C::RESPLIT) setmaxnreg_inc<C::REGS_SOFTMAX>();
+        const int half = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;
         const int t = q0 + r;
-        const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-        const uint32_t tS = tmem_base + lane_sel + C::COL_S;
-        const uint32_t tO = tmem_base + lane_sel + C::COL_O;
+        constexpr int OC = HD / 2;  // output columns per thread
+        const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tS = tmem_base + lane_sel + C::COL_S + half * 64;
+        const uint32_t tO = tmem_base + lane_sel + C::COL_O + half * OC;
         const float sl = p.scale_log2;
 
         int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
@@ -404,30 +389,52 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
         }
         const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
         const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
-
-        float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
-        float l = 0.f;
-        bool ok = true;
-        uint32_t va[32], vb[32];  // two chunk buffers: one is processed while the other loads
         const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
 
+        float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
+        float l = 0.f;            // this thread's share of the row sum
+        bool ok = true;
+        uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
+
         for (int i = 0; i < n_my; ++i) {
-            const int key0 = (my_lo + i) * C::BN;
+            const int kc = (my_lo + i) * C::BN + half * 64;
 #ifdef ARC_PREFILL_TRACE
             const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
             if (tr) p.trace[i * 8 + 0] = clock64();
 #endif
-            if (!mbar_wait_warp(s_full, i & 1)) {
+            if (ok && !mbar_wait_warp(s_full, i & 1)) {
                 report_fault(p.fault, FAULT_WAIT_S, i);
                 ok = false;
-                break;
+            }
+            if (!ok) {
+                // Gave up on a wait: keep meeting the partner warp at the pair barrier so it can
+                // never be left waiting there, but touch nothing else.
+                pair_sync(warp & 3);
+                continue;
             }
             tc_fence_after_sync();
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 8 + 1] = clock64();
 #endif
-            const float m_blk = has_mask ? row_block_max<true>(tS, va, vb, sl, key0, rm)
-                                         : row_block_max<false>(tS, va, vb, sl, key0, rm);
+            tmem_ld32(tS, va);
+            tmem_ld32(tS + 32, vb);
+            tmem_wait_ld();
+
+            // Maximum of this thread's 64 scores, then of the whole row via shared memory.
+            float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (has_mask) {
+                chunk_max_any<true>(va, mr, ms, sl, kc, rm);
+                chunk_max_any<true>(vb, mr, ms, sl, kc + 32, rm);
+            } else {
+                chunk_max_any<false>(va, mr, ms, sl, kc, rm);
+                chunk_max_any<false>(vb, mr, ms, sl, kc + 32, rm);
+            }
+            const float m_half = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                       fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+            xch_max[((i & 1) * 2 + half) * 128 + r] = m_half;
+            pair_sync(warp & 3);
+            const float m_blk = fmaxf(m_half, xch_max[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 8 + 2] = clock64();
 #endif
@@ -437,25 +444,42 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             } else {
                 const bool need = m_new > m + 8.0f;
                 if (__any_sync(0xffffffffu, need)) {
-                    // Rare: the row maximum grew by more than 2^8; rescale O in tensor memory.
+                    // Rare: the row maximum grew by more than 2^8; rescale this thread's half of
+                    // O in tensor memory (its partner takes the same decision from the same values),
+                    // then fetch the scores again.
                     const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
-                    tmem_wait_ld();
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
-                        tmem_ld32(tO + c * 32, vb);
+                    for (int c = 0; c < OC / 32; ++c) {
+                        tmem_ld32(tO + c * 32, va);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) vb[e] = __float_as_uint(__uint_as_float(vb[e]) * alpha);
-                        tmem_st32(tO + c * 32, vb);
+                        for (int e = 0; e < 32; ++e) va[e] = __float_as_uint(__uint_as_float(va[e]) * alpha);
+                        tmem_st32(tO + c * 32, va);
                     }
                     l *= alpha;
                     m = m_new;
+                    tmem_ld32(tS, va);
+                    tmem_wait_ld();
                 }
             }
             const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
 
-            l += has_mask ? row_block_exp<true>(tS, va, vb, sl, m_eff, key0, rm)
-                          : row_block_exp<false>(tS, va, vb, sl, m_eff, key0, rm);
+            // Probabilities as bf16 over the first 32 of this thread's S columns (all 64 scores
+            // are already in registers), row-sum share in fp32.
+            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[16];
+            if (has_mask) {
+                chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+                tmem_st16(tS, pk);
+                chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                tmem_st16(tS + 16, pk);
+            } else {
+                chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+                tmem_st16(tS, pk);
+                chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                tmem_st16(tS + 16, pk);
+            }
+            l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 8 + 3] = clock64();
 #endif
@@ -467,6 +491,10 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
 #endif
         }
 
+        // Row sum = both halves' shares.
+        xch_sum[half * 128 + r] = l;
+        pair_sync(warp & 3);
+        l += xch_sum[(half ^ 1) * 128 + r];
         if (ok && !mbar_wait_warp(o_full, 0)) {
             report_fault(p.fault, FAULT_WAIT_O, 0);
             ok = false;
@@ -478,9 +506,9 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
             const long long row = ((long long)b * p.seq + t) * p.nq + h;
             const bool store = t < p.seq;
             if (p.num_splits > 1) {
-                float* dst = p.part_o + ((long long)split * rows_total + row) * HD;
+                float* dst = p.part_o + ((long long)split * rows_total + row) * HD + half * OC;
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
                     if (store) {
@@ -491,13 +519,13 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                                             __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
                     }
                 }
-                if (store) p.part_lse[(long long)split * rows_total + row] = lse;
+                if (store && half == 0) p.part_lse[(long long)split * rows_total + row] = lse;
             } else {
-                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD;
+                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD + half * OC;
                 uint16_t* dst = p.out + eoff;
                 const uint16_t* g = p.gate ? p.gate + eoff : nullptr;
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
                     if (store) {
@@ -525,14 +553,14 @@ __global__ void __launch_bounds__(PrefillCfg<HD>::THREADS, PrefillCfg<HD>::MIN_C
                         }
                     }
                 }
-                if (store && p.out_lse) p.out_lse[row] = lse;
+                if (store && half == 0 && p.out_lse) p.out_lse[row] = lse;
             }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 8) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
 }  // namespace arc
