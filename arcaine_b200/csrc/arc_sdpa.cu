@@ -213,16 +213,7 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.out_lse = nullptr;
 #endif
 
-    // hd128: a CTA takes two tiles that share all their K/V blocks — the two query heads of
-    // a GQA pair when the group size is even, else two consecutive token tiles.
-    constexpr int NT = PrefillCfg<HD>::NT;
-    const int group = p->nq / p->nkv;
-    kp.pair_heads = (NT == 2 && group % 2 == 0) ? 1 : 0;
-    dim3 grid;
-    if (NT == 2 && kp.pair_heads)
-        grid = dim3((unsigned)plan.q_tiles, (unsigned)(p->nq / 2), (unsigned)(p->batch * plan.splits));
-    else
-        grid = dim3((unsigned)((plan.q_tiles + NT - 1) / NT), (unsigned)p->nq, (unsigned)(p->batch * plan.splits));
+    dim3 grid((unsigned)plan.q_tiles, (unsigned)p->nq, (unsigned)(p->batch * plan.splits));
     sdpa_prefill_kernel<HD><<<grid, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());

@@ -1,15 +1,15 @@
 // GQA flash-attention prefill / canvas kernel for sm_100a.
 //
-// One CTA owns one or two tiles of 128 query tokens of one query head each and
-// walks the key blocks (128 keys) those tiles can see.  Q, K and V tiles are staged in shared
+// One CTA owns a tile of 128 query tokens of one query head and walks the key
+// blocks (128 keys) that tile can see.  Q, K and V tiles are staged in shared
 // memory by TMA (128-byte swizzle, one 64-element column chunk per copy);
 // S = Q K^T and O += P V run on the tcgen05 tensor cores with both accumulators
 // in tensor memory; P is written back to tensor memory as bf16 over the S
 // columns and fed to the second MMA from there, so probabilities never touch
 // shared or global memory.  Softmax is online, fp32, one query row per thread.
 //
-// Warp roles: per tile eight softmax / correction / epilogue warps, two threads per
-// query row (warp index mod 4 selects the 32 TMEM lanes, the next bit the key half
+// Warp roles: sixteen softmax / correction / epilogue warps, four threads per query
+// row (warp index mod 4 selects the 32 TMEM lanes, warp index / 4 the 32-key quarter
 // of each block), then one TMA producer warp (also the TMEM owner) and one MMA
 // issuing warp.
 //
@@ -42,34 +42,33 @@ struct PrefillParams {
     float scale_log2;  // scale * log2(e)
     int mask_type, window;
     int num_splits;
-    int pair_heads;  // NT == 2: 1 = the CTA's tiles are query heads 2y, 2y+1; 0 = token tiles 2x, 2x+1
 #ifdef ARC_PREFILL_TRACE
     long long* trace;  // debug builds only: per-block timestamps of CTA 0
 #endif
 };
 
-// NT = query tiles (128 rows each) one CTA works on.  hd128 pairs two tiles that
-// share every K/V block (two query heads of one KV head, or two consecutive token
-// tiles) on one SM: both S/O accumulator sets fill the 512 TMEM columns, and a
-// single MMA-issuing thread alternates between the tiles, so one tile's softmax
-// always runs under the other tile's MMAs.  hd256 has room for one tile.
+// One CTA = one tile of 128 query tokens of one query head.  The score accumulator is
+// double buffered in tensor memory (S0, S1, then O), so S(u+1) = Q K(u+1)^T is computed
+// while the softmax warps work on S(u); sixteen softmax warps (four threads per query
+// row, 32 keys each) keep the exp unit busy.
 template <int HD>
 struct PrefillCfg {
-    static constexpr int NT = (HD == 128) ? 2 : 1;
     static constexpr int BM = 128;  // query rows per tile
     static constexpr int BN = 128;  // keys per block
     static constexpr int CH = HD / 64;
     static constexpr int CHUNK_BYTES = 128 * 128;  // 128 rows x 64 bf16
     static constexpr int TILE_BYTES = CH * CHUNK_BYTES;
-    static constexpr int STAGES = (HD == 128) ? 2 : 1;  // K and V ring depth
+    static constexpr int K_STAGES = (HD == 128) ? 3 : 1;
+    static constexpr int V_STAGES = (HD == 128) ? 2 : 1;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int TILE_COLS = 128 + HD;  // per tile: S (128 fp32 columns, P aliases them) then O
-    static constexpr int NUM_BARS = 1 + 4 * STAGES + 3 * NT;
-    static constexpr int XCH_FLOATS = 2 * 2 * 128 + 2 * 128;  // per tile: row-max exchange (2 phases) + row-sum exchange
-    static constexpr int SMEM_BYTES = (NT + 2 * STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + NT * XCH_FLOATS * 4 + 1024;
-    static constexpr int SOFTMAX_WARPS = 8 * NT;  // two threads per query row
+    static constexpr int COL_S = 0;    // two buffers of 128 fp32 columns; P (bf16) is written over them
+    static constexpr int COL_O = 256;  // HD fp32 columns
+    static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 + 2 + 1 + 1;
+    static constexpr int XCH_FLOATS = 2 * 4 * 128 + 4 * 128;  // row-max exchange (2 phases) + row-sum exchange
+    static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
+    static constexpr int SOFTMAX_WARPS = 16;
     static constexpr int THREADS = 32 * (SOFTMAX_WARPS + 2);
-    static constexpr int MAX_REGS = (NT == 2) ? 96 : 168;  // 65536 registers over the warps of a CTA, allocated four warps at a time
+    static constexpr int MAX_REGS = 96;  // 65536 registers over 20 allocated warps
 };
 
 // Per-row visibility for blocks that need element masking.
@@ -95,6 +94,20 @@ __device__ __forceinline__ float masked_score(uint32_t raw, float sl, int key, c
         if (rm.mask_row && key < rm.kv_len) x += rm.mask_row[key] * 1.4426950408889634f;
     }
     return (key >= rm.lo && key < rm.hi) ? x : -CUDART_INF_F;
+}
+
+// 2^x for x <= ~100 without the special-function unit: split off the integer part with the
+// 1.5 * 2^23 rounding trick, a degree-3 minimax polynomial for 2^f on [-0.5, 0.5], and the
+// integer part added straight into the exponent field.  Inputs below -125 are clamped (the
+// result is then ~2^-125, which rounds to a bf16 of no consequence).
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.0551716610789299f, 0.2426111251115799f);
+    p = fmaf(f, p, 0.6932609677314758f);
+    p = fmaf(f, p, 0.9999280571937561f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 // Maximum of one 32-column chunk, folded into four independent running maxima.
@@ -129,8 +142,13 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk
             p0 = fast_exp2(masked_score<MODE>(v[e], sl, key0 + e, rm) - m_eff);
             p1 = fast_exp2(masked_score<MODE>(v[e + 1], sl, key0 + e + 1, rm) - m_eff);
         } else {
+            // One of every sixteen exponentials is evaluated on the FMA pipe (degree-3 polynomial,
+            // relative error 7.5e-5, far below bf16 resolution).  The softmax is bound almost
+            // equally by the quarter-rate ex2 unit and by instruction issue, so only a small
+            // share can move before issue becomes the limit.
             p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, -m_eff));
-            p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
+            p1 = ((e >> 1) & 7) == 5 ? poly_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff))
+                                     : fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
         }
         ls[(e >> 1) & 3] += p0 + p1;
         pk[e >> 1] = pack_bf16x2(p0, p1);
@@ -173,52 +191,13 @@ __device__ __forceinline__ void chunk_exp_any(const uint32_t (&v)[32], uint32_t 
 }
 
 
-// Barrier between the two warps that share a set of 32 query rows of one tile: hardware
-// barrier `id`, 64 threads.  Every softmax warp of an active tile executes exactly one
-// pair_sync per key block and one after the loop, whatever happened to its waits, so
-// neither warp of a pair can be left waiting here.
-__device__ __forceinline__ void pair_sync(int id) {
-    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
-}
 
-// Geometry of one query tile of a CTA.
-struct TileGeom {
-    int q0;     // first query token
-    int head;   // query head
-    int lo, n;  // key blocks [lo, lo + n) this tile (and split) walks; n == 0: nothing to do
-    bool valid; // tile exists (token tiles: the last CTA of an odd count has one tile only)
-};
-
-template <int HD>
-__device__ __forceinline__ TileGeom tile_geometry(const PrefillParams& p, int x, int split) {
-    using C = PrefillCfg<HD>;
-    TileGeom g;
-    if (C::NT == 2 && p.pair_heads) {
-        g.q0 = blockIdx.x * C::BM;
-        g.head = blockIdx.y * 2 + x;
-    } else {
-        g.q0 = (blockIdx.x * C::NT + x) * C::BM;
-        g.head = blockIdx.y;
-    }
-    g.valid = g.q0 < p.seq;
-    g.lo = 0;
-    g.n = 0;
-    if (!g.valid) return g;
-    const int off = p.kv_len - p.seq;
-    const bool causal = (p.mask_type == 3);
-    const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
-    const int q_last = min(g.q0 + C::BM - 1, p.seq - 1);
-    int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
-    if (causal) {
-        const int last_key = min(p.kv_len - 1, q_last + off);
-        blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
-        if (windowed) blk_lo = max(0, g.q0 + off - p.window + 1) / C::BN;
-    }
-    const int nblk = max(0, blk_hi - blk_lo);
-    const int per = (nblk + p.num_splits - 1) / p.num_splits;
-    g.lo = blk_lo + split * per;
-    g.n = max(0, min(blk_hi, g.lo + per) - g.lo);
-    return g;
+// Barrier among the four warps that share a set of 32 query rows (warps q, q+4, q+8, q+12):
+// hardware barrier 1 + q, 128 threads.  Every softmax warp executes exactly one quad_sync per
+// key block and one after the loop, whatever happened to its waits, so none of the four can
+// be left waiting here.
+__device__ __forceinline__ void quad_sync(int quarter) {
+    asm volatile("bar.sync %0, 128;" ::"r"(quarter + 1) : "memory");
 }
 
 template <int HD>
@@ -226,85 +205,96 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
     using C = PrefillCfg<HD>;
-    constexpr int NT = C::NT;
-    constexpr int ST = C::STAGES;
+    constexpr int KS = C::K_STAGES;
+    constexpr int VS = C::V_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;                              // [NT] tiles
-    uint8_t* sK = smem + NT * C::TILE_BYTES;         // [ST] stages
-    uint8_t* sV = sK + ST * C::TILE_BYTES;           // [ST] stages
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + ST * C::TILE_BYTES);
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + C::TILE_BYTES;       // [KS] stages
+    uint8_t* sV = sK + KS * C::TILE_BYTES;    // [VS] stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VS * C::TILE_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
-    uint64_t* k_empty = k_full + ST;
-    uint64_t* v_full = k_empty + ST;
-    uint64_t* v_empty = v_full + ST;
-    uint64_t* s_full = v_empty + ST;  // [NT]
-    uint64_t* p_full = s_full + NT;   // [NT]
-    uint64_t* o_full = p_full + NT;   // [NT]
+    uint64_t* k_empty = k_full + KS;
+    uint64_t* v_full = k_empty + KS;
+    uint64_t* v_empty = v_full + VS;
+    uint64_t* s_full = v_empty + VS;  // [2] score buffers
+    uint64_t* p_full = s_full + 2;    // [2]
+    uint64_t* pv_done = p_full + 2;   // one phase per key block: O += P V of that block has completed
+    uint64_t* o_full = pv_done + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
-    float* xch = reinterpret_cast<float*>(tmem_slot + 4);  // per tile: max [2][2][128], sum [2][128]
+    float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][quarter-of-keys 4][row 128]
+    float* xch_sum = xch_max + 2 * 4 * 128;                    // [quarter-of-keys 4][row 128]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int qt = blockIdx.x;
+    const int h = blockIdx.y;
     const int b = blockIdx.z / p.num_splits;
     const int split = blockIdx.z % p.num_splits;
-    const long long rows_total = (long long)p.batch * p.seq * p.nq;
+    const int kvh = h / (p.nq / p.nkv);
+    const int q0 = qt * C::BM;
+    const int off = p.kv_len - p.seq;
+    const bool causal = (p.mask_type == 3);
+    const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
+    const int q_last = min(q0 + C::BM - 1, p.seq - 1);
 
-    TileGeom tg[NT];
-    int u_lo = 0x7fffffff, u_hi = 0;  // union of the tiles' block ranges
-#pragma unroll
-    for (int x = 0; x < NT; ++x) {
-        tg[x] = tile_geometry<HD>(p, x, split);
-        if (tg[x].n > 0) {
-            u_lo = min(u_lo, tg[x].lo);
-            u_hi = max(u_hi, tg[x].lo + tg[x].n);
-        }
+    // Key blocks [blk_lo, blk_hi) this tile can see, then this split's share.
+    int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
+    if (causal) {
+        int last_key = min(p.kv_len - 1, q_last + off);
+        blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
+        if (windowed) blk_lo = max(0, q0 + off - p.window + 1) / C::BN;
     }
-    const int n_u = max(0, u_hi - u_lo);
-    const int kvh = tg[0].head / (p.nq / p.nkv);  // both tiles share the KV head
+    const int nblk = max(0, blk_hi - blk_lo);
+    const int per = (nblk + p.num_splits - 1) / p.num_splits;
+    const int my_lo = blk_lo + split * per;
+    const int my_hi = min(blk_hi, my_lo + per);
+    const int n_my = max(0, my_hi - my_lo);
+
+    const long long rows_total = (long long)p.batch * p.seq * p.nq;
 
     if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
     __syncthreads();
     if (*abort_slot) return;
 
-    // Tiles with nothing visible: zero output (or an empty partial), written by the first
-    // four warps of the tile's softmax group.
-#pragma unroll
-    for (int x = 0; x < NT; ++x) {
-        if (tg[x].valid && tg[x].n == 0 && warp >= 8 * x && warp < 8 * x + 4) {
-            const int t = tg[x].q0 + (warp & 3) * 32 + lane;
+    if (n_my == 0) {
+        // Nothing visible: zero output (or an empty partial) for this tile.
+        if (warp < 4) {
+            const int t = q0 + threadIdx.x;
             if (t < p.seq) {
-                const long long row = ((long long)b * p.seq + t) * p.nq + tg[x].head;
+                const long long row = ((long long)b * p.seq + t) * p.nq + h;
                 if (p.num_splits > 1) {
                     float4* dst = reinterpret_cast<float4*>(p.part_o + ((long long)split * rows_total + row) * HD);
                     for (int i = 0; i < HD / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                     p.part_lse[(long long)split * rows_total + row] = -CUDART_INF_F;
                 } else {
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + b * p.o_stride_b + t * p.o_stride_t +
-                                                          (long long)tg[x].head * HD);
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD);
                     for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
                     if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
                 }
             }
         }
+        return;
     }
-    if (n_u == 0) return;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < ST; ++s) {
+        for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
+        }
+        for (int s = 0; s < VS; ++s) {
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
-        for (int x = 0; x < NT; ++x) {
-            mbar_init(&s_full[x], 1);
-            mbar_init(&p_full[x], 256);
-            mbar_init(&o_full[x], 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&p_full[s], 32 * C::SOFTMAX_WARPS);
         }
+        mbar_init(pv_done, 1);
+        mbar_init(o_full, 1);
         fence_mbar_init();
     }
     constexpr int PRODUCER_WARP = C::SOFTMAX_WARPS;
@@ -324,65 +314,69 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             prefetch_tensormap(&tm_q);
             prefetch_tensormap(&tm_k);
             prefetch_tensormap(&tm_v);
-            int n_q = 0;
+            mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
 #pragma unroll
-            for (int x = 0; x < NT; ++x) n_q += (tg[x].n > 0) ? 1 : 0;
-            mbar_arrive_expect_tx(q_full, n_q * C::TILE_BYTES);
-#pragma unroll
-            for (int x = 0; x < NT; ++x) {
-                if (tg[x].n > 0) {
+            for (int c = 0; c < C::CH; ++c) tma_load_4d(sQ + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, h, q0, b);
+            // K runs up to K_STAGES blocks ahead of the MMAs, V up to V_STAGES; the two rings
+            // are filled in the order the MMAs will need them.
+            int uk = 0, uv = 0;
+            bool ok = true;
+            while (ok && (uk < n_my || uv < n_my)) {
+                if (uk < n_my && (uk <= uv + 1 || uv >= n_my)) {
+                    const int st = uk % KS;
+                    if (uk >= KS && !mbar_wait(&k_empty[st], ((uk / KS) - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u + uk);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
 #pragma unroll
                     for (int c = 0; c < C::CH; ++c)
-                        tma_load_4d(sQ + x * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, tg[x].head,
-                                    tg[x].q0, b);
-                }
-            }
-            for (int u = 0; u < n_u; ++u) {
-                const int st = u % ST;
-                const int key0 = (u_lo + u) * C::BN;
-                if (u >= ST && !mbar_wait(&k_empty[st], ((u / ST) - 1) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u + u);
-                    break;
-                }
-                mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
+                        tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, kvh,
+                                    (my_lo + uk) * C::BN, b);
+                    ++uk;
+                } else {
+                    const int st = uv % VS;
+                    if (uv >= VS && !mbar_wait(&v_empty[st], ((uv / VS) - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u + uv);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
 #pragma unroll
-                for (int c = 0; c < C::CH; ++c)
-                    tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, kvh, key0, b);
-                if (u >= ST && !mbar_wait(&v_empty[st], ((u / ST) - 1) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u + u);
-                    break;
+                    for (int c = 0; c < C::CH; ++c)
+                        tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, kvh,
+                                    (my_lo + uv) * C::BN, b);
+                    ++uv;
                 }
-                mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
-#pragma unroll
-                for (int c = 0; c < C::CH; ++c)
-                    tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, kvh, key0, b);
             }
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
-        // One thread issues, for every key block u of the union range and every tile x that
-        // sees it:  O_x += P_x(u) V(u)  followed at once by  S_x = Q_x K(u+1)^T.  With two
-        // tiles the tensor pipe therefore runs tile A's pair of MMAs, then tile B's, and so
-        // on, and each tile's softmax has the other tile's MMA time to finish.
+        // Issue order: S(0); then for every block u:  S(u+1) = Q K(u+1)^T into the other score
+        // buffer (runs while the softmax warps work on S(u)), then O += P(u) V(u) once P(u) is in
+        // tensor memory.
         if (lane == 0) {
             constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
+            const uint32_t tO = tmem_base + C::COL_O;
             const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-            int done[NT];  // blocks of tile x whose PV has been issued
-#pragma unroll
-            for (int x = 0; x < NT; ++x) done[x] = 0;
-            auto sees = [&](int x, int u) {
-                return tg[x].n > 0 && u_lo + u >= tg[x].lo && u_lo + u < tg[x].lo + tg[x].n;
-            };
-            auto issue_qk = [&](int x, int st) {
-                const uint32_t tS = tmem_base + x * C::TILE_COLS;
+            // Descriptors are built once; per MMA only the start-address field (bytes >> 4, low
+            // word) moves, so the issuing thread needs a handful of instructions per MMA even
+            // when it shares its scheduler with four busy softmax warps.
+            const uint64_t dQ = make_smem_desc_sw128(aQ, 16, 1024);
+            const uint64_t dK = make_smem_desc_sw128(aK, 16, 1024);
+            const uint64_t dV = make_smem_desc_sw128(aV, C::CHUNK_BYTES, 1024);
+            auto issue_qk = [&](int u) {
+                const uint32_t tS = tmem_base + C::COL_S + (u & 1) * 128;
+                const uint64_t dKu = dK + (uint64_t)(((u % KS) * C::TILE_BYTES) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t o = (kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32;
-                    umma_ss(tS, make_smem_desc_sw128(aQ + x * C::TILE_BYTES + o, 16, 1024),
-                            make_smem_desc_sw128(aK + st * C::TILE_BYTES + o, 16, 1024), IDESC_QK, kk > 0 ? 1u : 0u);
+                    const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;
+                    umma_ss(tS, dQ + o, dKu + o, IDESC_QK, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[x]);
+                umma_commit(&s_full[u & 1]);
+                umma_commit(&k_empty[u % KS]);
             };
             bool ok = mbar_wait(q_full, 0);
             if (!ok) report_fault(p.fault, FAULT_WAIT_Q, 0);
@@ -392,181 +386,135 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             }
             if (ok) {
                 tc_fence_after_sync();
-#pragma unroll
-                for (int x = 0; x < NT; ++x)
-                    if (sees(x, 0)) issue_qk(x, 0);
-                umma_commit(&k_empty[0]);
+                issue_qk(0);
             }
-            for (int u = 0; ok && u < n_u; ++u) {
-                const int st = u % ST;
-                const int st1 = (u + 1) % ST;
-                bool v_ready = false, k_ready = false;
-#pragma unroll
-                for (int x = 0; x < NT; ++x) {
-                    if (ok && sees(x, u)) {
-                        if (!mbar_wait(&p_full[x], done[x] & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_P, u);
-                            ok = false;
-                        }
-#ifdef ARC_PREFILL_TRACE
-                        if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16)
-                            p.trace[u * 16 + 11 + 2 * x] = clock64();
-#endif
-                        if (ok && !v_ready) {
-                            if (!mbar_wait(&v_full[st], (u / ST) & 1)) {
-                                report_fault(p.fault, FAULT_WAIT_V, u);
-                                ok = false;
-                            }
-                            v_ready = true;
-                        }
-                        if (ok) {
-                            tc_fence_after_sync();
-                            // P from tensor memory, 8 columns per 16 keys; the two key halves of a
-                            // block keep their P at the start of their own S columns (keys 0-63 at
-                            // columns 0-31, keys 64-127 at columns 64-95).  V is MN-major: 64-element
-                            // head-dim chunks 16 KB apart (leading offset), 8-key groups 1024 bytes
-                            // apart (stride offset).
-                            const uint32_t tS = tmem_base + x * C::TILE_COLS;
-                            const uint32_t tO = tS + 128;
-#pragma unroll
-                            for (int ks = 0; ks < C::BN / 16; ++ks) {
-                                const uint32_t pcol = (ks < 4) ? ks * 8 : 64 + (ks - 4) * 8;
-                                umma_ts(tO, tS + pcol,
-                                        make_smem_desc_sw128(aV + st * C::TILE_BYTES + ks * 2048, C::CHUNK_BYTES, 1024),
-                                        IDESC_PV, (done[x] > 0 || ks > 0) ? 1u : 0u);
-                            }
-                            ++done[x];
-                            if (done[x] == tg[x].n) umma_commit(&o_full[x]);
-                        }
+            for (int u = 0; ok && u < n_my; ++u) {
+                if (u + 1 < n_my) {
+                    if (!mbar_wait(&k_full[(u + 1) % KS], ((u + 1) / KS) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_K, u + 1);
+                        break;
                     }
-                    if (ok && u + 1 < n_u && sees(x, u + 1)) {
-                        if (!k_ready) {
-                            if (!mbar_wait(&k_full[st1], ((u + 1) / ST) & 1)) {
-                                report_fault(p.fault, FAULT_WAIT_K, u + 1);
-                                ok = false;
-                            }
-                            k_ready = true;
-                        }
-                        if (ok) {
-                            tc_fence_after_sync();
-                            issue_qk(x, st1);
+                    tc_fence_after_sync();
+                    issue_qk(u + 1);
+                }
 #ifdef ARC_PREFILL_TRACE
-                            if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16)
-                                p.trace[u * 16 + 12 + 2 * x] = clock64();
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 11] = clock64();
 #endif
-                        }
-                    }
+                if (!mbar_wait(&p_full[u & 1], (u >> 1) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_P, u);
+                    break;
                 }
-                if (ok) {
-                    umma_commit(&v_empty[st]);
-                    if (u + 1 < n_u) umma_commit(&k_empty[st1]);
+#ifdef ARC_PREFILL_TRACE
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 12] = clock64();
+#endif
+                if (!mbar_wait(&v_full[u % VS], (u / VS) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_V, u);
+                    break;
                 }
+                tc_fence_after_sync();
+                // P from tensor memory: each 32-key quarter keeps its 16 bf16x2 columns at the start
+                // of its own 32 score columns, so 16 keys = 8 columns at 32*(ks/2) + 8*(ks%2).  V is
+                // MN-major: 64-element head-dim chunks 16 KB apart (leading offset), 8-key groups
+                // 1024 bytes apart (stride offset).
+                const uint32_t tS = tmem_base + C::COL_S + (u & 1) * 128;
+                const uint64_t dVu = dV + (uint64_t)(((u % VS) * C::TILE_BYTES) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < C::BN / 16; ++ks) {
+                    umma_ts(tO, tS + (ks >> 1) * 32 + (ks & 1) * 8, dVu + (uint64_t)((ks * 2048) >> 4), IDESC_PV,
+                            (u > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&v_empty[u % VS]);
+                umma_commit(pv_done);
+#ifdef ARC_PREFILL_TRACE
+                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 13] = clock64();
+#endif
             }
+            umma_commit(o_full);
         }
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
-        // Two threads per query row: warps 0-3 of a tile's group own keys 0-63 of every block
-        // (S columns 0-63), warps 4-7 keys 64-127; both halves of a row sit in the same TMEM lane.
-        const int x = warp >> 3;            // tile of this warp
-        const int half = (warp >> 2) & 1;   // key half
-        const int quarter = warp & 3;       // TMEM lane quarter
-        const TileGeom g = tg[x < NT ? x : 0];
-        if (g.n > 0) {
-            const int pair_id = 1 + x * 4 + quarter;
-            const int r = quarter * 32 + lane;
-            const int t = g.q0 + r;
-            constexpr int OC = HD / 2;  // output columns per thread
-            const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
-            const uint32_t tS = tmem_base + lane_sel + x * C::TILE_COLS + half * 64;
-            const uint32_t tO = tmem_base + lane_sel + x * C::TILE_COLS + 128 + half * OC;
-            float* xch_max = xch + x * C::XCH_FLOATS;  // [phase 2][half 2][row 128]
-            float* xch_sum = xch_max + 2 * 2 * 128;    // [half 2][row 128]
-            const float sl = p.scale_log2;
-            const int off = p.kv_len - p.seq;
-            const bool causal = (p.mask_type == 3);
-            const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
+        // Four threads per query row: warps 4c .. 4c+3 own keys [32c, 32c+32) of every block
+        // (score columns 32c .. 32c+31); all four threads of a row sit in the same TMEM lane.
+        const int kq = warp >> 2;       // 32-key quarter of each block
+        const int quarter = warp & 3;   // TMEM lane quarter
+        const int r = quarter * 32 + lane;
+        const int t = q0 + r;
+        constexpr int OC = HD / 4;  // output columns per thread
+        const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t tS0 = tmem_base + lane_sel + C::COL_S + kq * 32;
+        const uint32_t tO = tmem_base + lane_sel + C::COL_O + kq * OC;
+        const float sl = p.scale_log2;
 
-            int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
-            if (causal) {
-                const int diag = t + off;
-                row_hi = min(max(diag + 1, 0), p.kv_len);
-                if (windowed) row_lo = max(0, diag - p.window + 1);
-                if (row_lo > row_hi) row_lo = row_hi;
+        int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
+        if (causal) {
+            const int diag = t + off;
+            row_hi = min(max(diag + 1, 0), p.kv_len);
+            if (windowed) row_lo = max(0, diag - p.window + 1);
+            if (row_lo > row_hi) row_lo = row_hi;
+        }
+        const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
+        const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
+        const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
+
+        float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
+        float l = 0.f;            // this thread's share of the row sum
+        bool ok = true;
+        uint32_t va[32];          // this thread's 32 scores of the current block
+
+        for (int i = 0; i < n_my; ++i) {
+            const int kc = (my_lo + i) * C::BN + kq * 32;
+            const uint32_t tS = tS0 + (i & 1) * 128;
+#ifdef ARC_PREFILL_TRACE
+            const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
+            if (tr) p.trace[i * 16 + 0] = clock64();
+#endif
+            if (ok && !mbar_wait_warp(&s_full[i & 1], (i >> 1) & 1)) {
+                report_fault(p.fault, FAULT_WAIT_S, i);
+                ok = false;
             }
-            const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
-            const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
-            const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
-
-            float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
-            float l = 0.f;            // this thread's share of the row sum
-            bool ok = true;
-            uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
-
-            for (int i = 0; i < g.n; ++i) {
-                const int kc = (g.lo + i) * C::BN + half * 64;
-#ifdef ARC_PREFILL_TRACE
-                const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
-                if (tr) p.trace[i * 16 + 0] = clock64();
-#endif
-                if (ok && !mbar_wait_warp(&s_full[x], i & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_S, i);
-                    ok = false;
-                }
-                if (!ok) {
-                    // Gave up on a wait: keep meeting the partner warp at the pair barrier so it
-                    // can never be left waiting there, but touch nothing else.
-                    pair_sync(pair_id);
-                    continue;
-                }
-                tc_fence_after_sync();
-#ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 1] = clock64();
-#endif
-#ifdef ARC_PREFILL_SKIP_SOFTMAX
-                // Experiment only: no softmax work at all, to time the TMA + MMA pipeline alone.
-                tc_fence_before_sync();
-                mbar_arrive(&p_full[x]);
-                pair_sync(pair_id);
+            if (!ok) {
+                // Gave up on a wait: keep meeting the other three warps at the barrier so they can
+                // never be left waiting there, but touch nothing else.
+                quad_sync(quarter);
                 continue;
-#endif
-                tmem_ld32(tS, va);
-                tmem_ld32(tS + 32, vb);
-                tmem_wait_ld();
+            }
+            tc_fence_after_sync();
 #ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 8] = clock64();
+            if (tr) p.trace[i * 16 + 1] = clock64();
 #endif
+            tmem_ld32(tS, va);
+            tmem_wait_ld();
 
-                // Maximum of this thread's 64 scores, then of the whole row via shared memory.
-                float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                if (has_mask) {
-                    chunk_max_any<true>(va, mr, ms, sl, kc, rm);
-                    chunk_max_any<true>(vb, mr, ms, sl, kc + 32, rm);
-                } else {
-                    chunk_max_any<false>(va, mr, ms, sl, kc, rm);
-                    chunk_max_any<false>(vb, mr, ms, sl, kc + 32, rm);
-                }
-                const float m_half = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
-                                           fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+            // Maximum of this thread's 32 scores, then of the whole row via shared memory.
+            float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (has_mask) chunk_max_any<true>(va, mr, ms, sl, kc, rm);
+            else chunk_max_any<false>(va, mr, ms, sl, kc, rm);
+            const float m_part = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                       fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+            float* xm = xch_max + (i & 1) * 512;
+            xm[kq * 128 + r] = m_part;
+            quad_sync(quarter);
+            const float m_blk = fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r]));
 #ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 9] = clock64();
+            if (tr) p.trace[i * 16 + 2] = clock64();
 #endif
-                xch_max[((i & 1) * 2 + half) * 128 + r] = m_half;
-                pair_sync(pair_id);
-                const float m_blk = fmaxf(m_half, xch_max[((i & 1) * 2 + (half ^ 1)) * 128 + r]);
-#ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 2] = clock64();
-#endif
-                const float m_new = fmaxf(m, m_blk);
-                if (i == 0) {
-                    m = m_new;
-                } else {
-                    const bool need = m_new > m + 8.0f;
-                    if (__any_sync(0xffffffffu, need)) {
-                        // Rare: the row maximum grew by more than 2^8; rescale this thread's half
-                        // of O in tensor memory (its partner takes the same decision from the same
-                        // values), then fetch the scores again.
-                        const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+            const float m_new = fmaxf(m, m_blk);
+            if (i == 0) {
+                m = m_new;
+            } else {
+                const bool need = m_new > m + 8.0f;
+                if (__any_sync(0xffffffffu, need)) {
+                    // Rare: the row maximum grew by more than 2^8.  Once O += P V of the previous
+                    // block has landed, rescale this thread's quarter of O in tensor memory (the
+                    // other three threads of the row take the same decision from the same values),
+                    // then fetch the scores again.
+                    const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                    if (!mbar_wait_warp(pv_done, (i - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_O, i);
+                        ok = false;
+                    } else {
+                        tc_fence_after_sync();
 #pragma unroll 1
                         for (int c = 0; c < OC / 32; ++c) {
                             tmem_ld32(tO + c * 32, va);
@@ -581,102 +529,92 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                         tmem_wait_ld();
                     }
                 }
-                const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-
-                // Probabilities as bf16 over the first 32 of this thread's S columns (all 64
-                // scores are already in registers), row-sum share in fp32.
-                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t pk[16];
-                if (has_mask) {
-                    chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
-                    tmem_st16(tS, pk);
-                    chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                    tmem_st16(tS + 16, pk);
-                } else {
-                    chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
-                    tmem_st16(tS, pk);
-#ifdef ARC_PREFILL_TRACE
-                    if (tr) p.trace[i * 16 + 10] = clock64();
-#endif
-                    chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                    tmem_st16(tS + 16, pk);
-                }
-                l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-#ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 3] = clock64();
-#endif
-                tmem_wait_st();
-                tc_fence_before_sync();
-                mbar_arrive(&p_full[x]);
-#ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 4] = clock64();
-#endif
             }
+            if (!ok) continue;  // the quad barrier of this block has been met already
+            const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
 
-            // Row sum = both halves' shares.
-            xch_sum[half * 128 + r] = l;
-            pair_sync(pair_id);
-            l += xch_sum[(half ^ 1) * 128 + r];
-            if (ok && !mbar_wait_warp(&o_full[x], 0)) {
-                report_fault(p.fault, FAULT_WAIT_O, 0);
-                ok = false;
-            }
-            tc_fence_after_sync();
-            if (ok) {
-                const float inv = l > 0.f ? 1.0f / l : 0.f;
-                const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
-                const long long row = ((long long)b * p.seq + t) * p.nq + g.head;
-                const bool store = t < p.seq;
-                if (p.num_splits > 1) {
-                    float* dst = p.part_o + ((long long)split * rows_total + row) * HD + half * OC;
+            // Probabilities as bf16 over the first 16 of this thread's 32 score columns, row-sum
+            // share in fp32.
+            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[16];
+            if (has_mask) chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+            else chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+            tmem_st16(tS, pk);
+            l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 16 + 3] = clock64();
+#endif
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&p_full[i & 1]);
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 16 + 4] = clock64();
+#endif
+        }
+
+        // Row sum = the four threads' shares.
+        xch_sum[kq * 128 + r] = l;
+        quad_sync(quarter);
+        l = (xch_sum[r] + xch_sum[128 + r]) + (xch_sum[256 + r] + xch_sum[384 + r]);
+        if (ok && !mbar_wait_warp(o_full, 0)) {
+            report_fault(p.fault, FAULT_WAIT_O, 0);
+            ok = false;
+        }
+        tc_fence_after_sync();
+        if (ok) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
+            const long long row = ((long long)b * p.seq + t) * p.nq + h;
+            const bool store = t < p.seq;
+            if (p.num_splits > 1) {
+                float* dst = p.part_o + ((long long)split * rows_total + row) * HD + kq * OC;
 #pragma unroll 1
-                    for (int c = 0; c < OC / 32; ++c) {
-                        tmem_ld32(tO + c * 32, va);
-                        tmem_wait_ld();
-                        if (store) {
+                for (int c = 0; c < OC / 32; ++c) {
+                    tmem_ld32(tO + c * 32, va);
+                    tmem_wait_ld();
+                    if (store) {
 #pragma unroll
-                            for (int e = 0; e < 32; e += 4)
-                                *reinterpret_cast<float4*>(dst + c * 32 + e) =
-                                    make_float4(__uint_as_float(va[e]) * inv, __uint_as_float(va[e + 1]) * inv,
-                                                __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
-                        }
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<float4*>(dst + c * 32 + e) =
+                                make_float4(__uint_as_float(va[e]) * inv, __uint_as_float(va[e + 1]) * inv,
+                                            __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
                     }
-                    if (store && half == 0) p.part_lse[(long long)split * rows_total + row] = lse;
-                } else {
-                    const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)g.head * HD + half * OC;
-                    uint16_t* dst = p.out + eoff;
-                    const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
+                }
+                if (store && kq == 0) p.part_lse[(long long)split * rows_total + row] = lse;
+            } else {
+                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD + kq * OC;
+                uint16_t* dst = p.out + eoff;
+                const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
 #pragma unroll 1
-                    for (int c = 0; c < OC / 32; ++c) {
-                        tmem_ld32(tO + c * 32, va);
-                        tmem_wait_ld();
-                        if (store) {
+                for (int c = 0; c < OC / 32; ++c) {
+                    tmem_ld32(tO + c * 32, va);
+                    tmem_wait_ld();
+                    if (store) {
 #pragma unroll
-                            for (int e = 0; e < 32; e += 8) {
-                                float o[8];
+                        for (int e = 0; e < 32; e += 8) {
+                            float o[8];
 #pragma unroll
-                                for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(va[e + u]) * inv;
-                                if (gp) {
-                                    const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e);
-                                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(va[e + u]) * inv;
+                            if (gp) {
+                                const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e);
+                                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-                                    for (int u = 0; u < 8; ++u) {
-                                        const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
-                                        const float sig = 1.0f / (1.0f + __expf(-gf));
-                                        o[u] = bf16_round(o[u]) * sig;
-                                    }
+                                for (int u = 0; u < 8; ++u) {
+                                    const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
+                                    const float sig = 1.0f / (1.0f + __expf(-gf));
+                                    o[u] = bf16_round(o[u]) * sig;
                                 }
-                                uint4 ov;
-                                ov.x = pack_bf16x2(o[0], o[1]);
-                                ov.y = pack_bf16x2(o[2], o[3]);
-                                ov.z = pack_bf16x2(o[4], o[5]);
-                                ov.w = pack_bf16x2(o[6], o[7]);
-                                *reinterpret_cast<uint4*>(dst + c * 32 + e) = ov;
                             }
+                            uint4 ov;
+                            ov.x = pack_bf16x2(o[0], o[1]);
+                            ov.y = pack_bf16x2(o[2], o[3]);
+                            ov.z = pack_bf16x2(o[4], o[5]);
+                            ov.w = pack_bf16x2(o[6], o[7]);
+                            *reinterpret_cast<uint4*>(dst + c * 32 + e) = ov;
                         }
                     }
-                    if (store && half == 0 && p.out_lse) p.out_lse[row] = lse;
                 }
+                if (store && kq == 0 && p.out_lse) p.out_lse[row] = lse;
             }
         }
     }
