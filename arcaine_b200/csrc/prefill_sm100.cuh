@@ -48,9 +48,10 @@ struct PrefillParams {
 };
 
 // One CTA = one tile of 128 query tokens of one query head.  The score accumulator is
-// double buffered in tensor memory (S0, S1, then O), so S(u+1) = Q K(u+1)^T is computed
-// while the softmax warps work on S(u); sixteen softmax warps (four threads per query
-// row, 32 keys each) keep the exp unit busy.
+// multi-buffered in tensor memory (S0, S1[, S2], then O), so S = Q K^T runs one or two key
+// blocks ahead of the softmax; sixteen softmax warps (four threads per query row, 32 keys
+// each) look at the next block's maximum before they exponentiate the current one, which
+// keeps the exp unit busy through the exchange of row maxima.
 template <int HD>
 struct PrefillCfg {
     static constexpr int BM = 128;  // query rows per tile
@@ -61,9 +62,10 @@ struct PrefillCfg {
     static constexpr int K_STAGES = (HD == 128) ? 3 : 1;
     static constexpr int V_STAGES = (HD == 128) ? 2 : 1;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int COL_S = 0;    // two buffers of 128 fp32 columns; P (bf16) is written over them
-    static constexpr int COL_O = 256;  // HD fp32 columns
-    static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 + 2 + 1 + 1;
+    static constexpr int NSB = (HD == 128) ? 3 : 2;  // score buffers: S = Q K^T runs NSB-1 blocks ahead of the softmax
+    static constexpr int COL_S = 0;                  // NSB buffers of 128 fp32 columns; P (bf16) is written over them
+    static constexpr int COL_O = NSB * 128;          // HD fp32 columns
+    static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 1;
     static constexpr int XCH_FLOATS = 2 * 4 * 128 + 4 * 128;  // row-max exchange (2 phases) + row-sum exchange
     static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 16;
@@ -218,9 +220,10 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     uint64_t* k_empty = k_full + KS;
     uint64_t* v_full = k_empty + KS;
     uint64_t* v_empty = v_full + VS;
-    uint64_t* s_full = v_empty + VS;  // [2] score buffers
-    uint64_t* p_full = s_full + 2;    // [2]
-    uint64_t* pv_done = p_full + 2;   // one phase per key block: O += P V of that block has completed
+    constexpr int NSB = C::NSB;
+    uint64_t* s_full = v_empty + VS;    // [NSB] score buffers
+    uint64_t* p_full = s_full + NSB;    // [NSB]
+    uint64_t* pv_done = p_full + NSB;   // one phase per key block: O += P V of that block has completed
     uint64_t* o_full = pv_done + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
@@ -289,7 +292,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NSB; ++s) {
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], 32 * C::SOFTMAX_WARPS);
         }
@@ -353,9 +356,9 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
-        // Issue order: S(0); then for every block u:  S(u+1) = Q K(u+1)^T into the other score
-        // buffer (runs while the softmax warps work on S(u)), then O += P(u) V(u) once P(u) is in
-        // tensor memory.
+        // Issue order: the first NSB-1 score blocks; then for every block u:  S(u+NSB-1) into the
+        // buffer P(u-1) just left (runs while the softmax warps work on S(u)), then
+        // O += P(u) V(u) once P(u) is in tensor memory.
         if (lane == 0) {
             constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
@@ -368,39 +371,43 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             const uint64_t dK = make_smem_desc_sw128(aK, 16, 1024);
             const uint64_t dV = make_smem_desc_sw128(aV, C::CHUNK_BYTES, 1024);
             auto issue_qk = [&](int u) {
-                const uint32_t tS = tmem_base + C::COL_S + (u & 1) * 128;
+                const uint32_t tS = tmem_base + C::COL_S + (u % NSB) * 128;
                 const uint64_t dKu = dK + (uint64_t)(((u % KS) * C::TILE_BYTES) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;
                     umma_ss(tS, dQ + o, dKu + o, IDESC_QK, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[u & 1]);
+                umma_commit(&s_full[u % NSB]);
                 umma_commit(&k_empty[u % KS]);
             };
             bool ok = mbar_wait(q_full, 0);
             if (!ok) report_fault(p.fault, FAULT_WAIT_Q, 0);
-            if (ok && !mbar_wait(&k_full[0], 0)) {
-                report_fault(p.fault, FAULT_WAIT_K, 0);
-                ok = false;
-            }
-            if (ok) {
+            // Fill all but one score buffer before the loop.
+            for (int u = 0; ok && u < NSB - 1 && u < n_my; ++u) {
+                if (!mbar_wait(&k_full[u % KS], (u / KS) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_K, u);
+                    ok = false;
+                    break;
+                }
                 tc_fence_after_sync();
-                issue_qk(0);
+                issue_qk(u);
             }
             for (int u = 0; ok && u < n_my; ++u) {
-                if (u + 1 < n_my) {
-                    if (!mbar_wait(&k_full[(u + 1) % KS], ((u + 1) / KS) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_K, u + 1);
+                const int nxt = u + NSB - 1;
+                if (nxt < n_my) {
+                    // The buffer S(nxt) goes to held P(u-1), whose MMA was issued one trip ago.
+                    if (!mbar_wait(&k_full[nxt % KS], (nxt / KS) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_K, nxt);
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_qk(u + 1);
+                    issue_qk(nxt);
                 }
 #ifdef ARC_PREFILL_TRACE
                 if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 11] = clock64();
 #endif
-                if (!mbar_wait(&p_full[u & 1], (u >> 1) & 1)) {
+                if (!mbar_wait(&p_full[u % NSB], (u / NSB) & 1)) {
                     report_fault(p.fault, FAULT_WAIT_P, u);
                     break;
                 }
@@ -416,7 +423,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 // of its own 32 score columns, so 16 keys = 8 columns at 32*(ks/2) + 8*(ks%2).  V is
                 // MN-major: 64-element head-dim chunks 16 KB apart (leading offset), 8-key groups
                 // 1024 bytes apart (stride offset).
-                const uint32_t tS = tmem_base + C::COL_S + (u & 1) * 128;
+                const uint32_t tS = tmem_base + C::COL_S + (u % NSB) * 128;
                 const uint64_t dVu = dV + (uint64_t)(((u % VS) * C::TILE_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < C::BN / 16; ++ks) {
@@ -460,95 +467,107 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         float l = 0.f;            // this thread's share of the row sum
         bool ok = true;
         uint32_t va[32];          // this thread's 32 scores of the current block
+        uint32_t vb[32];          // scratch: next block's scores while their maximum is taken
+
+        // Partial maximum of block u over this thread's 32 keys, published for the row's other
+        // three threads.  Returns false if the scores never arrived.
+        auto publish_max = [&](int u) -> bool {
+            if (!mbar_wait_warp(&s_full[u % NSB], (u / NSB) & 1)) {
+                report_fault(p.fault, FAULT_WAIT_S, u);
+                return false;
+            }
+            tc_fence_after_sync();
+            tmem_ld32(tS0 + (u % NSB) * 128, vb);
+            tmem_wait_ld();
+            const int kc = (my_lo + u) * C::BN + kq * 32;
+            float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (has_mask) chunk_max_any<true>(vb, mr, ms, sl, kc, rm);
+            else chunk_max_any<false>(vb, mr, ms, sl, kc, rm);
+            xch_max[(u & 1) * 512 + kq * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                                         fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+            return true;
+        };
+
+        // Block 0: publish, meet, adopt the row maximum, fetch the scores.
+        ok = publish_max(0);
+        quad_sync(quarter);
+        if (ok) {
+            m = fmaxf(fmaxf(xch_max[r], xch_max[128 + r]), fmaxf(xch_max[256 + r], xch_max[384 + r]));
+            tmem_ld32(tS0, va);
+            tmem_wait_ld();
+        }
 
         for (int i = 0; i < n_my; ++i) {
             const int kc = (my_lo + i) * C::BN + kq * 32;
-            const uint32_t tS = tS0 + (i & 1) * 128;
+            const uint32_t tS = tS0 + (i % NSB) * 128;
+            const bool have_next = i + 1 < n_my;
 #ifdef ARC_PREFILL_TRACE
             const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
             if (tr) p.trace[i * 16 + 0] = clock64();
 #endif
-            if (ok && !mbar_wait_warp(&s_full[i & 1], (i >> 1) & 1)) {
-                report_fault(p.fault, FAULT_WAIT_S, i);
-                ok = false;
-            }
-            if (!ok) {
-                // Gave up on a wait: keep meeting the other three warps at the barrier so they can
-                // never be left waiting there, but touch nothing else.
-                quad_sync(quarter);
-                continue;
-            }
-            tc_fence_after_sync();
+            // The next block's scores were computed one or two blocks ago: take their maximum now,
+            // so that the exchange through shared memory is hidden behind this block's exponentials.
+            if (ok && have_next) ok = publish_max(i + 1);
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 16 + 1] = clock64();
 #endif
-            tmem_ld32(tS, va);
-            tmem_wait_ld();
-
-            // Maximum of this thread's 32 scores, then of the whole row via shared memory.
-            float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            if (has_mask) chunk_max_any<true>(va, mr, ms, sl, kc, rm);
-            else chunk_max_any<false>(va, mr, ms, sl, kc, rm);
-            const float m_part = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
-                                       fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
-            float* xm = xch_max + (i & 1) * 512;
-            xm[kq * 128 + r] = m_part;
-            quad_sync(quarter);
-            const float m_blk = fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r]));
+            if (ok) {
+                // Probabilities of block i as bf16 over the first 16 of this thread's 32 score
+                // columns, row-sum share in fp32.
+                const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t pk[16];
+                if (has_mask) chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+                else chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+                tmem_st16(tS, pk);
+                l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
 #ifdef ARC_PREFILL_TRACE
-            if (tr) p.trace[i * 16 + 2] = clock64();
+                if (tr) p.trace[i * 16 + 3] = clock64();
 #endif
-            const float m_new = fmaxf(m, m_blk);
-            if (i == 0) {
-                m = m_new;
-            } else {
-                const bool need = m_new > m + 8.0f;
-                if (__any_sync(0xffffffffu, need)) {
-                    // Rare: the row maximum grew by more than 2^8.  Once O += P V of the previous
-                    // block has landed, rescale this thread's quarter of O in tensor memory (the
-                    // other three threads of the row take the same decision from the same values),
-                    // then fetch the scores again.
-                    const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
-                    if (!mbar_wait_warp(pv_done, (i - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_O, i);
-                        ok = false;
-                    } else {
-                        tc_fence_after_sync();
-#pragma unroll 1
-                        for (int c = 0; c < OC / 32; ++c) {
-                            tmem_ld32(tO + c * 32, va);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (int e = 0; e < 32; ++e) va[e] = __float_as_uint(__uint_as_float(va[e]) * alpha);
-                            tmem_st32(tO + c * 32, va);
-                        }
-                        l *= alpha;
-                        m = m_new;
-                        tmem_ld32(tS, va);
-                        tmem_wait_ld();
-                    }
-                }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&p_full[i % NSB]);
+                if (have_next) tmem_ld32(tS0 + ((i + 1) % NSB) * 128, va);  // lands during the barrier below
             }
-            if (!ok) continue;  // the quad barrier of this block has been met already
-            const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-
-            // Probabilities as bf16 over the first 16 of this thread's 32 score columns, row-sum
-            // share in fp32.
-            float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t pk[16];
-            if (has_mask) chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
-            else chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
-            tmem_st16(tS, pk);
-            l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-#ifdef ARC_PREFILL_TRACE
-            if (tr) p.trace[i * 16 + 3] = clock64();
-#endif
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&p_full[i & 1]);
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 16 + 4] = clock64();
+#endif
+            if (!have_next) break;
+            // Every softmax warp meets here exactly once per block boundary, whatever happened to
+            // its waits, so none of the four warps of a row quarter can be left waiting.
+            quad_sync(quarter);
+            if (!ok) continue;
+            const float* xm = xch_max + ((i + 1) & 1) * 512;
+            const float m_new = fmaxf(m, fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r])));
+            const bool need = m_new > m + 8.0f;
+            if (__any_sync(0xffffffffu, need)) {
+                // Rare: the row maximum grows by more than 2^8 with block i+1.  Once O += P V of
+                // block i has landed, rescale this thread's quarter of O in tensor memory (the other
+                // three threads of the row take the same decision from the same values).
+                const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                tmem_wait_ld();
+                if (!mbar_wait_warp(pv_done, i & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_O, i);
+                    ok = false;
+                    continue;
+                }
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = 0; c < OC / 32; ++c) {
+                    tmem_ld32(tO + c * 32, vb);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) vb[e] = __float_as_uint(__uint_as_float(vb[e]) * alpha);
+                    tmem_st32(tO + c * 32, vb);
+                }
+                tmem_wait_st();
+                l *= alpha;
+                m = m_new;
+            }
+            tmem_wait_ld();
+#ifdef ARC_PREFILL_TRACE
+            if (tr) p.trace[i * 16 + 2] = clock64();
 #endif
         }
 
