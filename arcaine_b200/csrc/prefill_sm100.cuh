@@ -8,10 +8,9 @@
 // columns and fed to the second MMA from there, so probabilities never touch
 // shared or global memory.  Softmax is online, fp32, one query row per thread.
 //
-// Warp roles: sixteen softmax / correction / epilogue warps, four threads per query
-// row (warp index mod 4 selects the 32 TMEM lanes, warp index / 4 the 32-key quarter
-// of each block), then one TMA producer warp (also the TMEM owner) and one MMA
-// issuing warp.
+// Warp roles: eight softmax / correction / epilogue warps, two threads per query row
+// (warp index mod 4 selects the 32 TMEM lanes, warp index / 4 the 64-key half of each
+// block), then one TMA producer warp (also the TMEM owner) and one MMA issuing warp.
 //
 // Masking follows the reference's rules evaluated inline instead of through a
 // (q_len, kv_len) f32 buffer: causal aligned bottom-right with an optional
@@ -49,9 +48,11 @@ struct PrefillParams {
 
 // One CTA = one tile of 128 query tokens of one query head.  The score accumulator is
 // multi-buffered in tensor memory (S0, S1[, S2], then O), so S = Q K^T runs one or two key
-// blocks ahead of the softmax; sixteen softmax warps (four threads per query row, 32 keys
+// blocks ahead of the softmax; eight softmax warps (two threads per query row, 64 keys
 // each) look at the next block's maximum before they exponentiate the current one, which
-// keeps the exp unit busy through the exchange of row maxima.
+// hides the exchange of row maxima.  Eight rather than sixteen softmax warps on purpose: the
+// single MMA-issuing thread shares an instruction scheduler with them, and with four busy
+// warps per scheduler it could not issue MMAs fast enough to keep the tensor pipe fed.
 template <int HD>
 struct PrefillCfg {
     static constexpr int BM = 128;  // query rows per tile
@@ -66,11 +67,11 @@ struct PrefillCfg {
     static constexpr int COL_S = 0;                  // NSB buffers of 128 fp32 columns; P (bf16) is written over them
     static constexpr int COL_O = NSB * 128;          // HD fp32 columns
     static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 1;
-    static constexpr int XCH_FLOATS = 2 * 4 * 128 + 4 * 128;  // row-max exchange (2 phases) + row-sum exchange
+    static constexpr int XCH_FLOATS = 2 * 2 * 128 + 2 * 128;  // row-max exchange (2 phases) + row-sum exchange
     static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
-    static constexpr int SOFTMAX_WARPS = 16;
+    static constexpr int SOFTMAX_WARPS = 8;
     static constexpr int THREADS = 32 * (SOFTMAX_WARPS + 2);
-    static constexpr int MAX_REGS = 96;  // 65536 registers over 20 allocated warps
+    static constexpr int MAX_REGS = 168;  // 65536 registers over 12 allocated warps
 };
 
 // Per-row visibility for blocks that need element masking.
@@ -194,12 +195,12 @@ __device__ __forceinline__ void chunk_exp_any(const uint32_t (&v)[32], uint32_t 
 
 
 
-// Barrier among the four warps that share a set of 32 query rows (warps q, q+4, q+8, q+12):
-// hardware barrier 1 + q, 128 threads.  Every softmax warp executes exactly one quad_sync per
-// key block and one after the loop, whatever happened to its waits, so none of the four can
-// be left waiting here.
-__device__ __forceinline__ void quad_sync(int quarter) {
-    asm volatile("bar.sync %0, 128;" ::"r"(quarter + 1) : "memory");
+// Barrier between the two warps that share a set of 32 query rows (warps q and q + 4):
+// hardware barrier 1 + q, 64 threads.  Every softmax warp executes exactly one pair_sync
+// before the loop, one per block boundary and one after the loop, whatever happened to its
+// waits, so neither warp of a pair can be left waiting here.
+__device__ __forceinline__ void pair_sync(int quarter) {
+    asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
 }
 
 template <int HD>
@@ -227,8 +228,8 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     uint64_t* o_full = pv_done + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
-    float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][quarter-of-keys 4][row 128]
-    float* xch_sum = xch_max + 2 * 4 * 128;                    // [quarter-of-keys 4][row 128]
+    float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][key half 2][row 128]
+    float* xch_sum = xch_max + 2 * 2 * 128;                    // [key half 2][row 128]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -440,16 +441,16 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         }
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
-        // Four threads per query row: warps 4c .. 4c+3 own keys [32c, 32c+32) of every block
-        // (score columns 32c .. 32c+31); all four threads of a row sit in the same TMEM lane.
-        const int kq = warp >> 2;       // 32-key quarter of each block
+        // Two threads per query row: warps 0-3 own keys 0-63 of every block (score columns
+        // 0-63), warps 4-7 keys 64-127; both threads of a row sit in the same TMEM lane.
+        const int kh = warp >> 2;       // 64-key half of each block
         const int quarter = warp & 3;   // TMEM lane quarter
         const int r = quarter * 32 + lane;
         const int t = q0 + r;
-        constexpr int OC = HD / 4;  // output columns per thread
+        constexpr int OC = HD / 2;  // output columns per thread
         const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t tS0 = tmem_base + lane_sel + C::COL_S + kq * 32;
-        const uint32_t tO = tmem_base + lane_sel + C::COL_O + kq * OC;
+        const uint32_t tS0 = tmem_base + lane_sel + C::COL_S + kh * 64;
+        const uint32_t tO = tmem_base + lane_sel + C::COL_O + kh * OC;
         const float sl = p.scale_log2;
 
         int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
@@ -466,40 +467,47 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
         float l = 0.f;            // this thread's share of the row sum
         bool ok = true;
-        uint32_t va[32];          // this thread's 32 scores of the current block
-        uint32_t vb[32];          // scratch: next block's scores while their maximum is taken
+        uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
 
-        // Partial maximum of block u over this thread's 32 keys, published for the row's other
-        // three threads.  Returns false if the scores never arrived.
+        // Partial maximum of block u over this thread's 64 keys, published for the row's other
+        // thread.  Returns false if the scores never arrived.
         auto publish_max = [&](int u) -> bool {
             if (!mbar_wait_warp(&s_full[u % NSB], (u / NSB) & 1)) {
                 report_fault(p.fault, FAULT_WAIT_S, u);
                 return false;
             }
             tc_fence_after_sync();
-            tmem_ld32(tS0 + (u % NSB) * 128, vb);
+            uint32_t wa[32], wb[32];
+            tmem_ld32(tS0 + (u % NSB) * 128, wa);
+            tmem_ld32(tS0 + (u % NSB) * 128 + 32, wb);
             tmem_wait_ld();
-            const int kc = (my_lo + u) * C::BN + kq * 32;
+            const int kc = (my_lo + u) * C::BN + kh * 64;
             float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            if (has_mask) chunk_max_any<true>(vb, mr, ms, sl, kc, rm);
-            else chunk_max_any<false>(vb, mr, ms, sl, kc, rm);
-            xch_max[(u & 1) * 512 + kq * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+            if (has_mask) {
+                chunk_max_any<true>(wa, mr, ms, sl, kc, rm);
+                chunk_max_any<true>(wb, mr, ms, sl, kc + 32, rm);
+            } else {
+                chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
+                chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
+            }
+            xch_max[(u & 1) * 256 + kh * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
                                                          fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
             return true;
         };
 
         // Block 0: publish, meet, adopt the row maximum, fetch the scores.
         ok = publish_max(0);
-        quad_sync(quarter);
+        pair_sync(quarter);
         if (ok) {
-            m = fmaxf(fmaxf(xch_max[r], xch_max[128 + r]), fmaxf(xch_max[256 + r], xch_max[384 + r]));
+            m = fmaxf(xch_max[r], xch_max[128 + r]);
             tmem_ld32(tS0, va);
+            tmem_ld32(tS0 + 32, vb);
             tmem_wait_ld();
         }
 
         for (int i = 0; i < n_my; ++i) {
-            const int kc = (my_lo + i) * C::BN + kq * 32;
+            const int kc = (my_lo + i) * C::BN + kh * 64;
             const uint32_t tS = tS0 + (i % NSB) * 128;
             const bool have_next = i + 1 < n_my;
 #ifdef ARC_PREFILL_TRACE
@@ -513,14 +521,22 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             if (tr) p.trace[i * 16 + 1] = clock64();
 #endif
             if (ok) {
-                // Probabilities of block i as bf16 over the first 16 of this thread's 32 score
-                // columns, row-sum share in fp32.
+                // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its own 32
+                // score columns; row-sum share in fp32.
                 const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
                 float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t pk[16];
-                if (has_mask) chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
-                else chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
-                tmem_st16(tS, pk);
+                if (has_mask) {
+                    chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS, pk);
+                    chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                    tmem_st16(tS + 32, pk);
+                } else {
+                    chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS, pk);
+                    chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                    tmem_st16(tS + 32, pk);
+                }
                 l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
 #ifdef ARC_PREFILL_TRACE
                 if (tr) p.trace[i * 16 + 3] = clock64();
@@ -528,23 +544,24 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&p_full[i % NSB]);
-                if (have_next) tmem_ld32(tS0 + ((i + 1) % NSB) * 128, va);  // lands during the barrier below
+                if (have_next) {  // lands during the barrier below
+                    tmem_ld32(tS0 + ((i + 1) % NSB) * 128, va);
+                    tmem_ld32(tS0 + ((i + 1) % NSB) * 128 + 32, vb);
+                }
             }
 #ifdef ARC_PREFILL_TRACE
             if (tr) p.trace[i * 16 + 4] = clock64();
 #endif
             if (!have_next) break;
-            // Every softmax warp meets here exactly once per block boundary, whatever happened to
-            // its waits, so none of the four warps of a row quarter can be left waiting.
-            quad_sync(quarter);
+            pair_sync(quarter);
             if (!ok) continue;
-            const float* xm = xch_max + ((i + 1) & 1) * 512;
-            const float m_new = fmaxf(m, fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r])));
+            const float* xm = xch_max + ((i + 1) & 1) * 256;
+            const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
             const bool need = m_new > m + 8.0f;
             if (__any_sync(0xffffffffu, need)) {
                 // Rare: the row maximum grows by more than 2^8 with block i+1.  Once O += P V of
-                // block i has landed, rescale this thread's quarter of O in tensor memory (the other
-                // three threads of the row take the same decision from the same values).
+                // block i has landed, rescale this thread's half of O in tensor memory (the row's
+                // other thread takes the same decision from the same values).
                 const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
                 tmem_wait_ld();
                 if (!mbar_wait_warp(pv_done, i & 1)) {
@@ -553,13 +570,14 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                     continue;
                 }
                 tc_fence_after_sync();
+                uint32_t w[32];
 #pragma unroll 1
                 for (int c = 0; c < OC / 32; ++c) {
-                    tmem_ld32(tO + c * 32, vb);
+                    tmem_ld32(tO + c * 32, w);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) vb[e] = __float_as_uint(__uint_as_float(vb[e]) * alpha);
-                    tmem_st32(tO + c * 32, vb);
+                    for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(__uint_as_float(w[e]) * alpha);
+                    tmem_st32(tO + c * 32, w);
                 }
                 tmem_wait_st();
                 l *= alpha;
@@ -571,10 +589,10 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
 #endif
         }
 
-        // Row sum = the four threads' shares.
-        xch_sum[kq * 128 + r] = l;
-        quad_sync(quarter);
-        l = (xch_sum[r] + xch_sum[128 + r]) + (xch_sum[256 + r] + xch_sum[384 + r]);
+        // Row sum = the two threads' shares.
+        xch_sum[kh * 128 + r] = l;
+        pair_sync(quarter);
+        l = xch_sum[r] + xch_sum[128 + r];
         if (ok && !mbar_wait_warp(o_full, 0)) {
             report_fault(p.fault, FAULT_WAIT_O, 0);
             ok = false;
@@ -586,7 +604,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             const long long row = ((long long)b * p.seq + t) * p.nq + h;
             const bool store = t < p.seq;
             if (p.num_splits > 1) {
-                float* dst = p.part_o + ((long long)split * rows_total + row) * HD + kq * OC;
+                float* dst = p.part_o + ((long long)split * rows_total + row) * HD + kh * OC;
 #pragma unroll 1
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
@@ -599,9 +617,9 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                                             __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
                     }
                 }
-                if (store && kq == 0) p.part_lse[(long long)split * rows_total + row] = lse;
+                if (store && kh == 0) p.part_lse[(long long)split * rows_total + row] = lse;
             } else {
-                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD + kq * OC;
+                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD + kh * OC;
                 uint16_t* dst = p.out + eoff;
                 const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
 #pragma unroll 1
@@ -633,7 +651,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                         }
                     }
                 }
-                if (store && kq == 0 && p.out_lse) p.out_lse[row] = lse;
+                if (store && kh == 0 && p.out_lse) p.out_lse[row] = lse;
             }
         }
     }
