@@ -157,7 +157,6 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillP
     if (p->mask_type != ARC_MASK_NONE && p->mask_type != ARC_MASK_EXPLICIT && p->mask_type != ARC_MASK_CAUSAL)
         return ARC_ERR_BAD_SHAPE;
     if (p->num_splits < 0) return ARC_ERR_BAD_SHAPE;
-    if ((long long)p->batch * p->nq > 65535LL * 64) return ARC_ERR_TOO_LARGE;
     plan->q_tiles = (p->seq + 127) / 128;
     plan->rows = (long long)p->batch * p->seq * p->nq;
     const int kv_blocks = (p->kv_len + 127) / 128;
@@ -174,7 +173,6 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillP
     }
     if (splits > kv_blocks) splits = kv_blocks;
     if (splits > 64) splits = 64;
-    if ((long long)p->batch * splits > 65535) return ARC_ERR_TOO_LARGE;
     plan->splits = splits;
     plan->ws_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
     return ARC_OK;
@@ -213,8 +211,13 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.out_lse = nullptr;
 #endif
 
-    dim3 grid((unsigned)plan.q_tiles, (unsigned)p->nq, (unsigned)(p->batch * plan.splits));
-    sdpa_prefill_kernel<HD><<<grid, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+    // Persistent grid: one CTA per SM (fewer if there are fewer tiles), tiles dealt round-robin.
+    kp.q_tiles = plan.q_tiles;
+    const long long total_tiles = (long long)plan.q_tiles * p->nq * p->batch * plan.splits;
+    if (total_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
+    kp.total_tiles = (int)total_tiles;
+    const unsigned ctas = (unsigned)(total_tiles < ds->sm_count ? total_tiles : ds->sm_count);
+    sdpa_prefill_kernel<HD><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
 

@@ -41,12 +41,17 @@ struct PrefillParams {
     float scale_log2;  // scale * log2(e)
     int mask_type, window;
     int num_splits;
+    int q_tiles;      // ceil(seq / 128)
+    int total_tiles;  // q_tiles * nq * batch * num_splits, dealt round-robin to the persistent CTAs
 #ifdef ARC_PREFILL_TRACE
     long long* trace;  // debug builds only: per-block timestamps of CTA 0
 #endif
 };
 
-// One CTA = one tile of 128 query tokens of one query head.  The score accumulator is
+// One CTA per SM, persistent: it takes tiles (128 query tokens of one query head) round-robin
+// and keeps its pipelines running across tile boundaries — the next tile's Q, K and V stream in
+// and its first score blocks are computed while the softmax warps still write the previous
+// tile's output.  The score accumulator is
 // multi-buffered in tensor memory (S0, S1[, S2], then O), so S = Q K^T runs one or two key
 // blocks ahead of the softmax; eight softmax warps (two threads per query row, 64 keys
 // each) look at the next block's maximum before they exponentiate the current one, which
@@ -66,7 +71,7 @@ struct PrefillCfg {
     static constexpr int NSB = (HD == 128) ? 3 : 2;  // score buffers: S = Q K^T runs NSB-1 blocks ahead of the softmax
     static constexpr int COL_S = 0;                  // NSB buffers of 128 fp32 columns; P (bf16) is written over them
     static constexpr int COL_O = NSB * 128;          // HD fp32 columns
-    static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 1;
+    static constexpr int NUM_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 2;
     static constexpr int XCH_FLOATS = 2 * 2 * 128 + 2 * 128;  // row-max exchange (2 phases) + row-sum exchange
     static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;
@@ -196,11 +201,79 @@ __device__ __forceinline__ void chunk_exp_any(const uint32_t (&v)[32], uint32_t 
 
 
 // Barrier between the two warps that share a set of 32 query rows (warps q and q + 4):
-// hardware barrier 1 + q, 64 threads.  Every softmax warp executes exactly one pair_sync
-// before the loop, one per block boundary and one after the loop, whatever happened to its
-// waits, so neither warp of a pair can be left waiting here.
+// hardware barrier 1 + q, 64 threads.  Every softmax warp executes the same number of
+// pair_syncs per tile, whatever happened to its waits, so neither warp of a pair can be left
+// waiting here.
 __device__ __forceinline__ void pair_sync(int quarter) {
     asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
+}
+
+// One unit of work of the persistent kernel.
+struct TileWork {
+    int q0, h, b, split, kvh;
+    int my_lo, n_my;  // key blocks [my_lo, my_lo + n_my) of this tile and split
+};
+
+// Position of a persistent CTA in the launch's tile list: tile w = ((z * nq) + h) * q_tiles + qt,
+// token tiles fastest (neighbouring CTAs share K/V blocks in L2), then query heads, then
+// z = batch * num_splits + split.  The cursor moves by gridDim.x tiles per step with carries
+// instead of dividing again.
+struct TileCursor {
+    int w, qt, h, z;
+    int dqt, dh, dz;
+    __device__ __forceinline__ void init(const PrefillParams& p) {
+        w = blockIdx.x;
+        qt = w % p.q_tiles;
+        const int rest = w / p.q_tiles;
+        h = rest % p.nq;
+        z = rest / p.nq;
+        const int step = gridDim.x;
+        dqt = step % p.q_tiles;
+        const int srest = step / p.q_tiles;
+        dh = srest % p.nq;
+        dz = srest / p.nq;
+    }
+    __device__ __forceinline__ void advance(const PrefillParams& p) {
+        w += gridDim.x;
+        qt += dqt;
+        int carry = qt >= p.q_tiles ? 1 : 0;
+        qt -= carry * p.q_tiles;
+        h += dh + carry;
+        carry = h >= p.nq ? 1 : 0;
+        h -= carry * p.nq;
+        z += dz + carry;
+    }
+};
+
+template <int HD>
+__device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const TileCursor& cur) {
+    using C = PrefillCfg<HD>;
+    TileWork t;
+    t.h = cur.h;
+    if (p.num_splits == 1) {
+        t.b = cur.z;
+        t.split = 0;
+    } else {
+        t.b = cur.z / p.num_splits;
+        t.split = cur.z % p.num_splits;
+    }
+    t.kvh = t.h / (p.nq / p.nkv);
+    t.q0 = cur.qt * C::BM;
+    const int off = p.kv_len - p.seq;
+    const bool causal = (p.mask_type == 3);
+    const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
+    const int q_last = min(t.q0 + C::BM - 1, p.seq - 1);
+    int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
+    if (causal) {
+        const int last_key = min(p.kv_len - 1, q_last + off);
+        blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
+        if (windowed) blk_lo = max(0, t.q0 + off - p.window + 1) / C::BN;
+    }
+    const int nblk = max(0, blk_hi - blk_lo);
+    const int per = (nblk + p.num_splits - 1) / p.num_splits;
+    t.my_lo = blk_lo + t.split * per;
+    t.n_my = max(0, min(blk_hi, t.my_lo + per) - t.my_lo);
+    return t;
 }
 
 template <int HD>
@@ -210,6 +283,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     using C = PrefillCfg<HD>;
     constexpr int KS = C::K_STAGES;
     constexpr int VS = C::V_STAGES;
+    constexpr int NSB = C::NSB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
@@ -217,15 +291,16 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     uint8_t* sV = sK + KS * C::TILE_BYTES;    // [VS] stages
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + VS * C::TILE_BYTES);
     uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;
+    uint64_t* q_empty = bars + 1;       // the tile's last S = Q K^T has completed: Q may be replaced
+    uint64_t* k_full = bars + 2;
     uint64_t* k_empty = k_full + KS;
     uint64_t* v_full = k_empty + KS;
     uint64_t* v_empty = v_full + VS;
-    constexpr int NSB = C::NSB;
     uint64_t* s_full = v_empty + VS;    // [NSB] score buffers
     uint64_t* p_full = s_full + NSB;    // [NSB]
     uint64_t* pv_done = p_full + NSB;   // one phase per key block: O += P V of that block has completed
-    uint64_t* o_full = pv_done + 1;
+    uint64_t* o_full = pv_done + 1;     // one phase per tile: the tile's last O += P V has completed
+    uint64_t* o_empty = o_full + 1;     // one phase per tile: the softmax warps have read O out
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
     float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][key half 2][row 128]
@@ -233,58 +308,18 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int qt = blockIdx.x;
-    const int h = blockIdx.y;
-    const int b = blockIdx.z / p.num_splits;
-    const int split = blockIdx.z % p.num_splits;
-    const int kvh = h / (p.nq / p.nkv);
-    const int q0 = qt * C::BM;
-    const int off = p.kv_len - p.seq;
+    const long long rows_total = (long long)p.batch * p.seq * p.nq;
     const bool causal = (p.mask_type == 3);
     const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
-    const int q_last = min(q0 + C::BM - 1, p.seq - 1);
-
-    // Key blocks [blk_lo, blk_hi) this tile can see, then this split's share.
-    int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
-    if (causal) {
-        int last_key = min(p.kv_len - 1, q_last + off);
-        blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
-        if (windowed) blk_lo = max(0, q0 + off - p.window + 1) / C::BN;
-    }
-    const int nblk = max(0, blk_hi - blk_lo);
-    const int per = (nblk + p.num_splits - 1) / p.num_splits;
-    const int my_lo = blk_lo + split * per;
-    const int my_hi = min(blk_hi, my_lo + per);
-    const int n_my = max(0, my_hi - my_lo);
-
-    const long long rows_total = (long long)p.batch * p.seq * p.nq;
+    const int off = p.kv_len - p.seq;
 
     if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
     __syncthreads();
     if (*abort_slot) return;
 
-    if (n_my == 0) {
-        // Nothing visible: zero output (or an empty partial) for this tile.
-        if (warp < 4) {
-            const int t = q0 + threadIdx.x;
-            if (t < p.seq) {
-                const long long row = ((long long)b * p.seq + t) * p.nq + h;
-                if (p.num_splits > 1) {
-                    float4* dst = reinterpret_cast<float4*>(p.part_o + ((long long)split * rows_total + row) * HD);
-                    for (int i = 0; i < HD / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    p.part_lse[(long long)split * rows_total + row] = -CUDART_INF_F;
-                } else {
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD);
-                    for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
-                }
-            }
-        }
-        return;
-    }
-
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
@@ -299,6 +334,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         }
         mbar_init(pv_done, 1);
         mbar_init(o_full, 1);
+        mbar_init(o_empty, 32 * C::SOFTMAX_WARPS);
         fence_mbar_init();
     }
     constexpr int PRODUCER_WARP = C::SOFTMAX_WARPS;
@@ -318,126 +354,143 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             prefetch_tensormap(&tm_q);
             prefetch_tensormap(&tm_k);
             prefetch_tensormap(&tm_v);
-            mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
-#pragma unroll
-            for (int c = 0; c < C::CH; ++c) tma_load_4d(sQ + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, h, q0, b);
-            // K runs up to K_STAGES blocks ahead of the MMAs, V up to V_STAGES; the two rings
-            // are filled in the order the MMAs will need them.
-            int uk = 0, uv = 0;
+            int gk = 0, gv = 0, tc = 0;  // K blocks, V blocks and non-empty tiles loaded so far
             bool ok = true;
-            while (ok && (uk < n_my || uv < n_my)) {
-                if (uk < n_my && (uk <= uv + 1 || uv >= n_my)) {
-                    const int st = uk % KS;
-                    if (uk >= KS && !mbar_wait(&k_empty[st], ((uk / KS) - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u + uk);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
-#pragma unroll
-                    for (int c = 0; c < C::CH; ++c)
-                        tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, kvh,
-                                    (my_lo + uk) * C::BN, b);
-                    ++uk;
-                } else {
-                    const int st = uv % VS;
-                    if (uv >= VS && !mbar_wait(&v_empty[st], ((uv / VS) - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u + uv);
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
-#pragma unroll
-                    for (int c = 0; c < C::CH; ++c)
-                        tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, kvh,
-                                    (my_lo + uv) * C::BN, b);
-                    ++uv;
+            TileCursor cur;
+            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+                const TileWork tw = decode_tile<HD>(p, cur);
+                if (tw.n_my == 0) continue;
+                if (tc > 0 && !mbar_wait(q_empty, (tc - 1) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_EMPTY, 0x300u);
+                    break;
                 }
+                mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
+#pragma unroll
+                for (int c = 0; c < C::CH; ++c) tma_load_4d(sQ + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, tw.h, tw.q0, tw.b);
+                // K runs up to K_STAGES blocks ahead of the MMAs, V up to V_STAGES; the two rings
+                // are filled in the order the MMAs will need them.
+                int uk = 0, uv = 0;
+                while (uk < tw.n_my || uv < tw.n_my) {
+                    if (uk < tw.n_my && (uk <= uv + 1 || uv >= tw.n_my)) {
+                        const int st = gk % KS;
+                        if (gk >= KS && !mbar_wait(&k_empty[st], ((gk / KS) - 1) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
+#pragma unroll
+                        for (int c = 0; c < C::CH; ++c)
+                            tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, tw.kvh,
+                                        (tw.my_lo + uk) * C::BN, tw.b);
+                        ++uk;
+                        ++gk;
+                    } else {
+                        const int st = gv % VS;
+                        if (gv >= VS && !mbar_wait(&v_empty[st], ((gv / VS) - 1) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
+#pragma unroll
+                        for (int c = 0; c < C::CH; ++c)
+                            tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, tw.kvh,
+                                        (tw.my_lo + uv) * C::BN, tw.b);
+                        ++uv;
+                        ++gv;
+                    }
+                }
+                ++tc;
             }
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
-        // Issue order: the first NSB-1 score blocks; then for every block u:  S(u+NSB-1) into the
+        // Per tile: the first NSB-1 score blocks; then for every block u:  S(u+NSB-1) into the
         // buffer P(u-1) just left (runs while the softmax warps work on S(u)), then
-        // O += P(u) V(u) once P(u) is in tensor memory.
+        // O += P(u) V(u) once P(u) is in tensor memory.  Counters run across tiles, so buffers,
+        // stages and barrier phases simply keep rotating.
         if (lane == 0) {
             constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
             constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
             const uint32_t tO = tmem_base + C::COL_O;
             const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
             // Descriptors are built once; per MMA only the start-address field (bytes >> 4, low
-            // word) moves, so the issuing thread needs a handful of instructions per MMA even
-            // when it shares its scheduler with four busy softmax warps.
+            // word) moves, so the issuing thread needs a handful of instructions per MMA.
             const uint64_t dQ = make_smem_desc_sw128(aQ, 16, 1024);
             const uint64_t dK = make_smem_desc_sw128(aK, 16, 1024);
             const uint64_t dV = make_smem_desc_sw128(aV, C::CHUNK_BYTES, 1024);
-            auto issue_qk = [&](int u) {
-                const uint32_t tS = tmem_base + C::COL_S + (u % NSB) * 128;
-                const uint64_t dKu = dK + (uint64_t)(((u % KS) * C::TILE_BYTES) >> 4);
+            int gs = 0, gp = 0, tc = 0;  // score blocks issued, P V blocks issued, non-empty tiles started
+            auto issue_qk = [&]() -> bool {
+                if (!mbar_wait(&k_full[gs % KS], (gs / KS) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_K, gs);
+                    return false;
+                }
+                tc_fence_after_sync();
+                const uint32_t tS = tmem_base + C::COL_S + (gs % NSB) * 128;
+                const uint64_t dKu = dK + (uint64_t)(((gs % KS) * C::TILE_BYTES) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;
                     umma_ss(tS, dQ + o, dKu + o, IDESC_QK, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(&s_full[u % NSB]);
-                umma_commit(&k_empty[u % KS]);
+                umma_commit(&s_full[gs % NSB]);
+                umma_commit(&k_empty[gs % KS]);
+                ++gs;
+                return true;
             };
-            bool ok = mbar_wait(q_full, 0);
-            if (!ok) report_fault(p.fault, FAULT_WAIT_Q, 0);
-            // Fill all but one score buffer before the loop.
-            for (int u = 0; ok && u < NSB - 1 && u < n_my; ++u) {
-                if (!mbar_wait(&k_full[u % KS], (u / KS) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_K, u);
-                    ok = false;
+            bool ok = true;
+            TileCursor cur;
+            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+                const TileWork tw = decode_tile<HD>(p, cur);
+                if (tw.n_my == 0) continue;
+                if (!mbar_wait(q_full, tc & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_Q, tc);
                     break;
                 }
-                tc_fence_after_sync();
-                issue_qk(u);
-            }
-            for (int u = 0; ok && u < n_my; ++u) {
-                const int nxt = u + NSB - 1;
-                if (nxt < n_my) {
-                    // The buffer S(nxt) goes to held P(u-1), whose MMA was issued one trip ago.
-                    if (!mbar_wait(&k_full[nxt % KS], (nxt / KS) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_K, nxt);
+                int issued = 0;  // score blocks of this tile issued so far
+                for (; ok && issued < NSB - 1 && issued < tw.n_my; ++issued) ok = issue_qk();
+                if (ok && issued == tw.n_my) umma_commit(q_empty);
+                for (int u = 0; ok && u < tw.n_my; ++u) {
+                    if (issued < tw.n_my) {
+                        ok = issue_qk();
+                        if (!ok) break;
+                        if (++issued == tw.n_my) umma_commit(q_empty);
+                    }
+                    if (!mbar_wait(&p_full[gp % NSB], (gp / NSB) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_P, gp);
+                        ok = false;
+                        break;
+                    }
+                    if (!mbar_wait(&v_full[gp % VS], (gp / VS) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_V, gp);
+                        ok = false;
+                        break;
+                    }
+                    if (u == 0 && tc > 0 && !mbar_wait(o_empty, (tc - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_O, 0x100u + tc);
+                        ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_qk(nxt);
-                }
-#ifdef ARC_PREFILL_TRACE
-                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 11] = clock64();
-#endif
-                if (!mbar_wait(&p_full[u % NSB], (u / NSB) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_P, u);
-                    break;
-                }
-#ifdef ARC_PREFILL_TRACE
-                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 12] = clock64();
-#endif
-                if (!mbar_wait(&v_full[u % VS], (u / VS) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_V, u);
-                    break;
-                }
-                tc_fence_after_sync();
-                // P from tensor memory: each 32-key quarter keeps its 16 bf16x2 columns at the start
-                // of its own 32 score columns, so 16 keys = 8 columns at 32*(ks/2) + 8*(ks%2).  V is
-                // MN-major: 64-element head-dim chunks 16 KB apart (leading offset), 8-key groups
-                // 1024 bytes apart (stride offset).
-                const uint32_t tS = tmem_base + C::COL_S + (u % NSB) * 128;
-                const uint64_t dVu = dV + (uint64_t)(((u % VS) * C::TILE_BYTES) >> 4);
+                    // P from tensor memory: each 32-key chunk keeps its 16 bf16x2 columns at the start
+                    // of its own 32 score columns, so 16 keys = 8 columns at 32*(ks/2) + 8*(ks%2).  V is
+                    // MN-major: 64-element head-dim chunks 16 KB apart (leading offset), 8-key groups
+                    // 1024 bytes apart (stride offset).
+                    const uint32_t tS = tmem_base + C::COL_S + (gp % NSB) * 128;
+                    const uint64_t dVu = dV + (uint64_t)(((gp % VS) * C::TILE_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < C::BN / 16; ++ks) {
-                    umma_ts(tO, tS + (ks >> 1) * 32 + (ks & 1) * 8, dVu + (uint64_t)((ks * 2048) >> 4), IDESC_PV,
-                            (u > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < C::BN / 16; ++ks) {
+                        umma_ts(tO, tS + (ks >> 1) * 32 + (ks & 1) * 8, dVu + (uint64_t)((ks * 2048) >> 4), IDESC_PV,
+                                (u > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&v_empty[gp % VS]);
+                    umma_commit(pv_done);
+                    ++gp;
                 }
-                umma_commit(&v_empty[u % VS]);
-                umma_commit(pv_done);
-#ifdef ARC_PREFILL_TRACE
-                if (p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && u < 16) p.trace[u * 16 + 13] = clock64();
-#endif
+                if (ok) umma_commit(o_full);
+                ++tc;
             }
-            umma_commit(o_full);
         }
     } else {
         // ------------------------------------------------------------------ softmax / epilogue
@@ -446,165 +499,192 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         const int kh = warp >> 2;       // 64-key half of each block
         const int quarter = warp & 3;   // TMEM lane quarter
         const int r = quarter * 32 + lane;
-        const int t = q0 + r;
         constexpr int OC = HD / 2;  // output columns per thread
         const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tS0 = tmem_base + lane_sel + C::COL_S + kh * 64;
         const uint32_t tO = tmem_base + lane_sel + C::COL_O + kh * OC;
         const float sl = p.scale_log2;
-
-        int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
-        if (causal) {
-            const int diag = t + off;
-            row_hi = min(max(diag + 1, 0), p.kv_len);
-            if (windowed) row_lo = max(0, diag - p.window + 1);
-            if (row_lo > row_hi) row_lo = row_hi;
-        }
         const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
-        const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
-        const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
 
-        float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
-        float l = 0.f;            // this thread's share of the row sum
+        int gb = 0, tc = 0;  // key blocks and non-empty tiles processed so far
         bool ok = true;
+#ifdef ARC_PREFILL_TRACE
+        int tpos = 0;
+        const bool tr = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
+#define ARC_TR(code) do { if (tr && tpos < 200) { p.trace[2 * tpos] = (code); p.trace[2 * tpos + 1] = clock64(); ++tpos; } } while (0)
+#else
+#define ARC_TR(code) do { } while (0)
+#endif
         uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
 
-        // Partial maximum of block u over this thread's 64 keys, published for the row's other
-        // thread.  Returns false if the scores never arrived.
-        auto publish_max = [&](int u) -> bool {
-            if (!mbar_wait_warp(&s_full[u % NSB], (u / NSB) & 1)) {
-                report_fault(p.fault, FAULT_WAIT_S, u);
-                return false;
-            }
-            tc_fence_after_sync();
-            uint32_t wa[32], wb[32];
-            tmem_ld32(tS0 + (u % NSB) * 128, wa);
-            tmem_ld32(tS0 + (u % NSB) * 128 + 32, wb);
-            tmem_wait_ld();
-            const int kc = (my_lo + u) * C::BN + kh * 64;
-            float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-            if (has_mask) {
-                chunk_max_any<true>(wa, mr, ms, sl, kc, rm);
-                chunk_max_any<true>(wb, mr, ms, sl, kc + 32, rm);
-            } else {
-                chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
-                chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
-            }
-            xch_max[(u & 1) * 256 + kh * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
-                                                         fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
-            return true;
-        };
-
-        // Block 0: publish, meet, adopt the row maximum, fetch the scores.
-        ok = publish_max(0);
-        pair_sync(quarter);
-        if (ok) {
-            m = fmaxf(xch_max[r], xch_max[128 + r]);
-            tmem_ld32(tS0, va);
-            tmem_ld32(tS0 + 32, vb);
-            tmem_wait_ld();
-        }
-
-        for (int i = 0; i < n_my; ++i) {
-            const int kc = (my_lo + i) * C::BN + kh * 64;
-            const uint32_t tS = tS0 + (i % NSB) * 128;
-            const bool have_next = i + 1 < n_my;
-#ifdef ARC_PREFILL_TRACE
-            const bool tr = p.trace && blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && i < 16;
-            if (tr) p.trace[i * 16 + 0] = clock64();
-#endif
-            // The next block's scores were computed one or two blocks ago: take their maximum now,
-            // so that the exchange through shared memory is hidden behind this block's exponentials.
-            if (ok && have_next) ok = publish_max(i + 1);
-#ifdef ARC_PREFILL_TRACE
-            if (tr) p.trace[i * 16 + 1] = clock64();
-#endif
-            if (ok) {
-                // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its own 32
-                // score columns; row-sum share in fp32.
-                const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t pk[16];
-                if (has_mask) {
-                    chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
-                    tmem_st16(tS, pk);
-                    chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                    tmem_st16(tS + 32, pk);
-                } else {
-                    chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
-                    tmem_st16(tS, pk);
-                    chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                    tmem_st16(tS + 32, pk);
+        TileCursor cur;
+        for (cur.init(p); cur.w < p.total_tiles; cur.advance(p)) {
+            const TileWork tw = decode_tile<HD>(p, cur);
+            const int t = tw.q0 + r;
+            const long long row = ((long long)tw.b * p.seq + t) * p.nq + tw.h;
+            if (tw.n_my == 0) {
+                // Nothing visible: zero output (or an empty partial) for this tile.
+                if (t < p.seq) {
+                    if (p.num_splits > 1) {
+                        float4* dst = reinterpret_cast<float4*>(p.part_o + ((long long)tw.split * rows_total + row) * HD + kh * OC);
+                        for (int i = 0; i < OC / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (kh == 0) p.part_lse[(long long)tw.split * rows_total + row] = -CUDART_INF_F;
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + tw.b * p.o_stride_b + t * p.o_stride_t +
+                                                              (long long)tw.h * HD + kh * OC);
+                        for (int i = 0; i < OC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        if (kh == 0 && p.out_lse) p.out_lse[row] = -CUDART_INF_F;
+                    }
                 }
-                l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-#ifdef ARC_PREFILL_TRACE
-                if (tr) p.trace[i * 16 + 3] = clock64();
-#endif
-                tmem_wait_st();
-                tc_fence_before_sync();
-                mbar_arrive(&p_full[i % NSB]);
-                if (have_next) {  // lands during the barrier below
-                    tmem_ld32(tS0 + ((i + 1) % NSB) * 128, va);
-                    tmem_ld32(tS0 + ((i + 1) % NSB) * 128 + 32, vb);
-                }
+                continue;
             }
-#ifdef ARC_PREFILL_TRACE
-            if (tr) p.trace[i * 16 + 4] = clock64();
-#endif
-            if (!have_next) break;
-            pair_sync(quarter);
-            if (!ok) continue;
-            const float* xm = xch_max + ((i + 1) & 1) * 256;
-            const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
-            const bool need = m_new > m + 8.0f;
-            if (__any_sync(0xffffffffu, need)) {
-                // Rare: the row maximum grows by more than 2^8 with block i+1.  Once O += P V of
-                // block i has landed, rescale this thread's half of O in tensor memory (the row's
-                // other thread takes the same decision from the same values).
-                const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
-                tmem_wait_ld();
-                if (!mbar_wait_warp(pv_done, i & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_O, i);
-                    ok = false;
-                    continue;
+
+            int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
+            if (causal) {
+                const int diag = t + off;
+                row_hi = min(max(diag + 1, 0), p.kv_len);
+                if (windowed) row_lo = max(0, diag - p.window + 1);
+                if (row_lo > row_hi) row_lo = row_hi;
+            }
+            const float* mask_row = has_mask && t < p.seq ? p.mask + (long long)t * p.kv_len : nullptr;
+            const RowMask rm{row_lo, row_hi, p.kv_len, mask_row};
+
+            float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
+            float l = 0.f;            // this thread's share of the row sum
+
+            // Partial maximum of the tile's block u (global block g = gb + u) over this thread's
+            // 64 keys, published for the row's other thread.  False if the scores never arrived.
+            // (The scores are fetched again for the exponentials: holding both blocks' 128 values
+            // in registers at once does not fit next to the working set.)
+            auto publish_max = [&](int u) -> bool {
+                const int g = gb + u;
+                if (!mbar_wait_warp(&s_full[g % NSB], (g / NSB) & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_S, g);
+                    return false;
                 }
                 tc_fence_after_sync();
-                uint32_t w[32];
-#pragma unroll 1
-                for (int c = 0; c < OC / 32; ++c) {
-                    tmem_ld32(tO + c * 32, w);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) w[e] = __float_as_uint(__uint_as_float(w[e]) * alpha);
-                    tmem_st32(tO + c * 32, w);
+                uint32_t wa[32], wb[32];
+                tmem_ld32(tS0 + (g % NSB) * 128, wa);
+                tmem_ld32(tS0 + (g % NSB) * 128 + 32, wb);
+                tmem_wait_ld();
+                const int kc = (tw.my_lo + u) * C::BN + kh * 64;
+                float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                if (has_mask) {
+                    chunk_max_any<true>(wa, mr, ms, sl, kc, rm);
+                    chunk_max_any<true>(wb, mr, ms, sl, kc + 32, rm);
+                } else {
+                    chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
+                    chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
                 }
-                tmem_wait_st();
-                l *= alpha;
-                m = m_new;
-            }
-            tmem_wait_ld();
-#ifdef ARC_PREFILL_TRACE
-            if (tr) p.trace[i * 16 + 2] = clock64();
-#endif
-        }
+                xch_max[(g & 1) * 256 + kh * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                                             fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+                return true;
+            };
 
-        // Row sum = the two threads' shares.
-        xch_sum[kh * 128 + r] = l;
-        pair_sync(quarter);
-        l = xch_sum[r] + xch_sum[128 + r];
-        if (ok && !mbar_wait_warp(o_full, 0)) {
-            report_fault(p.fault, FAULT_WAIT_O, 0);
-            ok = false;
-        }
-        tc_fence_after_sync();
-        if (ok) {
+            ARC_TR(1000 + tw.n_my);  // tile start
+            // Block 0: publish, meet, adopt the row maximum, fetch the scores.
+            if (ok) ok = publish_max(0);
+            pair_sync(quarter);
+            if (ok) {
+                const float* xm = xch_max + (gb & 1) * 256;
+                m = fmaxf(xm[r], xm[128 + r]);
+                tmem_ld32(tS0 + (gb % NSB) * 128, va);
+                tmem_ld32(tS0 + (gb % NSB) * 128 + 32, vb);
+                tmem_wait_ld();
+            }
+
+            for (int i = 0; i < tw.n_my; ++i) {
+                const int g = gb + i;
+                const int kc = (tw.my_lo + i) * C::BN + kh * 64;
+                const uint32_t tS = tS0 + (g % NSB) * 128;
+                const bool have_next = i + 1 < tw.n_my;
+                // The next block's scores were computed one or two blocks ago: take their maximum
+                // now, so that the exchange through shared memory is hidden behind this block's
+                // exponentials.
+                ARC_TR(10);  // block start
+                if (ok && have_next) ok = publish_max(i + 1);
+                ARC_TR(11);  // next max published
+                if (ok) {
+                    // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its
+                    // own 32 score columns; row-sum share in fp32.
+                    const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+                    float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint32_t pk[16];
+                    if (has_mask) {
+                        chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+                        tmem_st16(tS, pk);
+                        chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                        tmem_st16(tS + 32, pk);
+                    } else {
+                        chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+                        tmem_st16(tS, pk);
+                        chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                        tmem_st16(tS + 32, pk);
+                    }
+                    l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&p_full[g % NSB]);
+                    ARC_TR(12);  // P arrived
+                    if (have_next) {  // lands during the barrier below
+                        tmem_ld32(tS0 + ((g + 1) % NSB) * 128, va);
+                        tmem_ld32(tS0 + ((g + 1) % NSB) * 128 + 32, vb);
+                    }
+                }
+                if (!have_next) break;
+                pair_sync(quarter);
+                if (!ok) continue;
+                const float* xm = xch_max + ((g + 1) & 1) * 256;
+                const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
+                const bool need = m_new > m + 8.0f;
+                if (__any_sync(0xffffffffu, need)) {
+                    // Rare: the row maximum grows by more than 2^8 with the next block.  Once
+                    // O += P V of block i has landed, rescale this thread's half of O in tensor
+                    // memory (the row's other thread takes the same decision from the same values).
+                    const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                    tmem_wait_ld();
+                    if (!mbar_wait_warp(pv_done, g & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_O, g);
+                        ok = false;
+                        continue;
+                    }
+                    tc_fence_after_sync();
+                    uint32_t ww[32];
+#pragma unroll 1
+                    for (int c = 0; c < OC / 32; ++c) {
+                        tmem_ld32(tO + c * 32, ww);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ww[e] = __float_as_uint(__uint_as_float(ww[e]) * alpha);
+                        tmem_st32(tO + c * 32, ww);
+                    }
+                    tmem_wait_st();
+                    l *= alpha;
+                    m = m_new;
+                }
+                tmem_wait_ld();
+            }
+            gb += tw.n_my;
+
+            // Row sum = the two threads' shares.
+            xch_sum[kh * 128 + r] = l;
+            pair_sync(quarter);
+            l = xch_sum[r] + xch_sum[128 + r];
+            ARC_TR(20);  // waiting for O
+            if (ok && !mbar_wait_warp(o_full, tc & 1)) {
+                report_fault(p.fault, FAULT_WAIT_O, tc);
+                ok = false;
+            }
+            ++tc;
+            if (!ok) continue;
+            tc_fence_after_sync();
+            ARC_TR(21);  // O complete
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
-            const long long row = ((long long)b * p.seq + t) * p.nq + h;
             const bool store = t < p.seq;
             if (p.num_splits > 1) {
-                float* dst = p.part_o + ((long long)split * rows_total + row) * HD + kh * OC;
+                float* dst = p.part_o + ((long long)tw.split * rows_total + row) * HD + kh * OC;
 #pragma unroll 1
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
@@ -617,42 +697,62 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                                             __uint_as_float(va[e + 2]) * inv, __uint_as_float(va[e + 3]) * inv);
                     }
                 }
-                if (store && kh == 0) p.part_lse[(long long)split * rows_total + row] = lse;
+                // O is in registers / on its way out: the next tile may overwrite the accumulator.
+                tc_fence_before_sync();
+                mbar_arrive(o_empty);
+                if (store && kh == 0) p.part_lse[(long long)tw.split * rows_total + row] = lse;
             } else {
-                const long long eoff = b * p.o_stride_b + t * p.o_stride_t + (long long)h * HD + kh * OC;
+                const long long eoff = tw.b * p.o_stride_b + t * p.o_stride_t + (long long)tw.h * HD + kh * OC;
                 uint16_t* dst = p.out + eoff;
                 const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
+                // One thread writes 128 (or 256) contiguous bytes of its row.  When the row is 32-byte
+                // aligned this goes out as 256-bit stores, each a whole DRAM sector.
+                const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
 #pragma unroll 1
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
+                    if (c == OC / 32 - 1) {
+                        tc_fence_before_sync();
+                        mbar_arrive(o_empty);
+                    }
                     if (store) {
 #pragma unroll
-                        for (int e = 0; e < 32; e += 8) {
-                            float o[8];
+                        for (int e = 0; e < 32; e += 16) {
+                            uint32_t ov[8];
 #pragma unroll
-                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(va[e + u]) * inv;
-                            if (gp) {
-                                const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e);
-                                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+                            for (int hh = 0; hh < 2; ++hh) {
+                                float o[8];
 #pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
-                                    const float sig = 1.0f / (1.0f + __expf(-gf));
-                                    o[u] = bf16_round(o[u]) * sig;
+                                for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(va[e + hh * 8 + u]) * inv;
+                                if (gp) {
+                                    const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e + hh * 8);
+                                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                                    for (int u = 0; u < 8; ++u) {
+                                        const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
+                                        const float sig = 1.0f / (1.0f + __expf(-gf));
+                                        o[u] = bf16_round(o[u]) * sig;
+                                    }
                                 }
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) ov[hh * 4 + u] = pack_bf16x2(o[2 * u], o[2 * u + 1]);
                             }
-                            uint4 ov;
-                            ov.x = pack_bf16x2(o[0], o[1]);
-                            ov.y = pack_bf16x2(o[2], o[3]);
-                            ov.z = pack_bf16x2(o[4], o[5]);
-                            ov.w = pack_bf16x2(o[6], o[7]);
-                            *reinterpret_cast<uint4*>(dst + c * 32 + e) = ov;
+                            uint16_t* q = dst + c * 32 + e;
+                            if (wide) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(ov[0]),
+                                             "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]), "r"(ov[6]), "r"(ov[7])
+                                             : "memory");
+                            } else {
+                                *reinterpret_cast<uint4*>(q) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                                *reinterpret_cast<uint4*>(q + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
+                            }
                         }
                     }
                 }
                 if (store && kh == 0 && p.out_lse) p.out_lse[row] = lse;
             }
+            ARC_TR(22);  // tile written
         }
     }
 
