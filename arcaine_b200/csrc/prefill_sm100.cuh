@@ -712,6 +712,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
+                    ARC_TR(23);  // O chunk in registers
                     if (c == OC / 32 - 1) {
                         tc_fence_before_sync();
                         mbar_arrive(o_empty);
