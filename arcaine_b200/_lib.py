@@ -34,7 +34,7 @@ STATIC_SCRATCH_BYTES = 8 << 20
 
 EXPORTS = (
     "arc_sdpa_status_string", "arc_sdpa_last_error", "arc_sdpa_prefill_workspace_bytes", "arc_sdpa_prefill",
-    "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
+    "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_exchange_bytes", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
     "arc_fill_causal_mask", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
 )
 
@@ -63,6 +63,7 @@ class DecodeParams(C.Structure):
         ("q_stride_b", C.c_int64), ("o_stride_b", C.c_int64), ("kv_stride_b", C.c_int64), ("kv_stride_t", C.c_int64), ("kv_rows_total", C.c_int64),
         ("scale", C.c_float), ("num_ctas", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("xchg_peers", C.c_void_p), ("xchg_world", C.c_int32), ("xchg_rank", C.c_int32), ("xchg_step", C.c_uint32),
     ]
 
 
@@ -92,6 +93,8 @@ def load() -> C.CDLL:
     L.arc_sdpa_decode_workspace_bytes.argtypes = [C.POINTER(DecodeParams)]
     L.arc_sdpa_decode.restype = C.c_int
     L.arc_sdpa_decode.argtypes = [C.POINTER(DecodeParams), vp]
+    L.arc_sdpa_exchange_bytes.restype = C.c_size_t
+    L.arc_sdpa_exchange_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
     L.arc_sdpa_decode_static.restype = C.c_int
     L.arc_sdpa_decode_static.argtypes = [C.POINTER(DecodeParams), vp]
     L.arc_sdpa_merge.restype = C.c_int

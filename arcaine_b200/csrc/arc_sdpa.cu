@@ -343,6 +343,11 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     mp.ncta = plan.ncta;
     mp.slices = plan.slices;
     mp.o_stride_b = p->o_stride_b;
+    mp.x_peers = reinterpret_cast<const unsigned long long*>(p->xchg_peers);
+    mp.x_world = p->xchg_world;
+    mp.x_rank = p->xchg_rank;
+    mp.x_step = p->xchg_step;
+    mp.fault = ds->fault;
     dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
     const size_t merge_smem = (size_t)(p->batch + 2) * 8 + 8 * sizeof(float) + (size_t)(MERGE_THREADS / 32) * HD * sizeof(float) +
                               (size_t)(plan.ncta + 1) * plan.slices * sizeof(float);  // a sequence spans at most ncta shares
@@ -420,6 +425,11 @@ extern "C" size_t arc_sdpa_decode_workspace_bytes(const arc_sdpa_decode_params* 
     return plan.ws_bytes;
 }
 
+extern "C" size_t arc_sdpa_exchange_bytes(int32_t world, int32_t batch, int32_t nq, int32_t hd) {
+    if (world <= 0 || batch <= 0 || nq <= 0 || hd <= 0) return 0;
+    return xchg_total_bytes(world, (long long)batch * nq, hd);
+}
+
 extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
     if (!p) return ARC_ERR_NULL_POINTER;
     if (!p->q || !p->k || !p->v) return ARC_ERR_NULL_POINTER;
@@ -436,6 +446,10 @@ extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
         p->q_stride_b < 0 || p->o_stride_b < 0 || p->kv_stride_b < 0)
         return ARC_ERR_ALIGNMENT;
     if (p->gate && !p->out) return ARC_ERR_NULL_POINTER;
+    if (p->xchg_world > 1) {
+        if (!p->xchg_peers || !p->out) return ARC_ERR_NULL_POINTER;
+        if (p->xchg_rank < 0 || p->xchg_rank >= p->xchg_world || p->xchg_world > MERGE_THREADS) return ARC_ERR_BAD_SHAPE;
+    }
     if (!p->workspace || p->workspace_bytes < plan.ws_bytes) return ARC_ERR_WORKSPACE_TOO_SMALL;
     if (!aligned16(p->workspace)) return ARC_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -359,7 +359,34 @@ struct DecodeMergeParams {
     int batch, nq, kv_len_uniform;
     int ncta, slices;
     long long o_stride_b;
+    // Sequence-sharded decode over NVLink peer memory (x_world > 1): every rank's exchange
+    // buffer base address; this rank's index; a step counter that grows by one per call.
+    const unsigned long long* x_peers;
+    int x_world, x_rank;
+    uint32_t x_step;
+    uint32_t* fault;
 };
+
+// Layout of one rank's exchange buffer: two parities x world sources x rows records, stored as
+// three arrays (out f32 [2][world][rows][hd], lse f32 [2][world][rows], flag u32 [2][world][rows]).
+__host__ __device__ inline size_t xchg_lse_offset(int world, long long rows, int hd) {
+    return (size_t)2 * world * rows * hd * sizeof(float);
+}
+__host__ __device__ inline size_t xchg_flag_offset(int world, long long rows, int hd) {
+    return xchg_lse_offset(world, rows, hd) + (size_t)2 * world * rows * sizeof(float);
+}
+__host__ __device__ inline size_t xchg_total_bytes(int world, long long rows, int hd) {
+    return xchg_flag_offset(world, rows, hd) + (size_t)2 * world * rows * sizeof(uint32_t);
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ float sigmoid_gate(float attn, uint16_t gate_bits) {
     const float g = bf16_bits_to_f32(gate_bits);
@@ -447,9 +474,9 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
     __syncthreads();
     const long long row = (long long)b * p.nq + h;
     if (p.out_lse && threadIdx.x == 0) p.out_lse[row] = lse;
+    const int d = threadIdx.x * 2;
+    float a0 = 0.f, a1 = 0.f;
     if (threadIdx.x < HD / 2) {
-        const int d = threadIdx.x * 2;
-        float a0 = 0.f, a1 = 0.f;
 #pragma unroll
         for (int w = 0; w < MERGE_THREADS / 32; ++w) {
             a0 += acc_sm[w * HD + d];
@@ -458,6 +485,68 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
         a0 *= inv;
         a1 *= inv;
         if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(a0, a1);
+    }
+    if (p.x_world > 1) {
+        // Sequence-sharded: this rank's (out, lse) of the row goes straight into every rank's
+        // exchange buffer over NVLink (plain peer stores), followed by a release-store of the step
+        // number into that rank's flag for (source, row).  Then the block waits — for a bounded
+        // time — until all sources' flags for its row show this step, and folds the records.
+        const long long rows = (long long)p.batch * p.nq;
+        const int par = (int)(p.x_step & 1u);
+        const size_t slot = ((size_t)par * p.x_world + p.x_rank) * rows + row;
+        for (int dst = 0; dst < p.x_world; ++dst) {
+            unsigned char* base = reinterpret_cast<unsigned char*>(p.x_peers[dst]);
+            if (threadIdx.x < HD / 2)
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(base) + slot * HD + d) = make_float2(a0, a1);
+            if (threadIdx.x == 0) reinterpret_cast<float*>(base + xchg_lse_offset(p.x_world, rows, HD))[slot] = lse;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < p.x_world) {
+            unsigned char* base = reinterpret_cast<unsigned char*>(p.x_peers[threadIdx.x]);
+            st_release_sys(reinterpret_cast<uint32_t*>(base + xchg_flag_offset(p.x_world, rows, HD)) + slot, p.x_step);
+        }
+        unsigned char* mine = reinterpret_cast<unsigned char*>(p.x_peers[p.x_rank]);
+        const float* r_out = reinterpret_cast<const float*>(mine);
+        const float* r_lse = reinterpret_cast<const float*>(mine + xchg_lse_offset(p.x_world, rows, HD));
+        const uint32_t* r_flag = reinterpret_cast<const uint32_t*>(mine + xchg_flag_offset(p.x_world, rows, HD));
+        __shared__ int x_timeout;
+        if (threadIdx.x == 0) x_timeout = 0;
+        __syncthreads();
+        if (threadIdx.x < p.x_world) {
+            const uint32_t* f = r_flag + ((size_t)par * p.x_world + threadIdx.x) * rows + row;
+            const long long t0 = clock64();
+            while ((int)(ld_acquire_sys(f) - p.x_step) < 0) {
+                if (clock64() - t0 > 2000000000LL) {  // about a second: the peer never came
+                    report_fault(p.fault, FAULT_WAIT_PEER, (uint32_t)threadIdx.x);
+                    x_timeout = 1;
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        if (x_timeout) return;
+        float mx = -CUDART_INF_F;
+        for (int src = 0; src < p.x_world; ++src) mx = fmaxf(mx, r_lse[((size_t)par * p.x_world + src) * rows + row]);
+        float z = 0.f, b0 = 0.f, b1 = 0.f;
+        if (mx > -CUDART_INF_F && threadIdx.x < HD / 2) {
+            for (int src = 0; src < p.x_world; ++src) {
+                const size_t sl = ((size_t)par * p.x_world + src) * rows + row;
+                const float li = r_lse[sl];
+                if (li == -CUDART_INF_F) continue;
+                const float wgt_s = __expf(li - mx);
+                z += wgt_s;
+                const float2 ov = *reinterpret_cast<const float2*>(r_out + sl * HD + d);
+                b0 = fmaf(wgt_s, ov.x, b0);
+                b1 = fmaf(wgt_s, ov.y, b1);
+            }
+            b0 /= z;
+            b1 /= z;
+        }
+        a0 = b0;
+        a1 = b1;
+    }
+    if (threadIdx.x < HD / 2) {
         if (p.out) {
             const long long eoff = (long long)b * p.o_stride_b + (long long)h * HD + d;
             if (p.gate) {

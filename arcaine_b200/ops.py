@@ -20,7 +20,7 @@ __all__ = [
     "sdpa_prefill", "sdpa_decode", "sdpa_merge", "mul_sigmoid_inplace", "fill_causal_mask",
     "gqa_attention_sdpa", "gqa_attention", "batched_attention", "qwen35_xmx_attention",
     "qwen35_online_attention", "qwen35_xmx_attention_decode_gqa",
-    "device_status", "clear_device_status", "launch_count", "Workspace",
+    "device_status", "clear_device_status", "launch_count", "Workspace", "exchange_bytes",
 ]
 
 
@@ -133,7 +133,7 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
                 gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, want_out: bool = True, num_ctas: int = 0,
                 partial_out: Optional[torch.Tensor] = None, partial_lse: Optional[torch.Tensor] = None,
-                workspace: Optional[Workspace] = None):
+                exchange: Optional[tuple] = None, workspace: Optional[Workspace] = None):
     """Split-KV decode of one query token per sequence.
 
     q: (B, nq, hd).  k, v: either (B, max_len, nkv, hd) (one cache block per sequence) or
@@ -141,6 +141,9 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
     ``kv_len``: int (same for all) or int32 device tensor (B,).
     Returns ``out`` (B, nq, hd) bf16; with ``return_partial`` also (out_f32, lse) — the
     ungated fp32 result and natural-log LSE a sequence-sharded caller exchanges.
+    ``exchange`` = (peer_ptrs int64 device tensor (world,), world, rank, step) turns on the
+    in-kernel exchange of those records over NVLink peer memory: ``out`` is then the result
+    merged over all ranks' key slices (see :class:`arcaine_b200.sharded.SeqShardedDecode`).
     """
     _require(q, torch.bfloat16, "q")
     _require(k, torch.bfloat16, "k")
@@ -219,6 +222,10 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
     p.batch, p.nq, p.nkv, p.hd = B, nq, nkv, hd
     p.q_stride_b = q.stride(0)
     p.scale, p.num_ctas = float(scale), int(num_ctas)
+    if exchange is not None:
+        peers, world, rank, step = exchange
+        _require(peers, torch.int64, "exchange peers")
+        p.xchg_peers, p.xchg_world, p.xchg_rank, p.xchg_step = peers.data_ptr(), int(world), int(rank), int(step) & 0xFFFFFFFF
     L_ = _lib.load()
     with torch.cuda.device(q.device):
         need = L_.arc_sdpa_decode_workspace_bytes(C.byref(p))
@@ -358,6 +365,11 @@ def qwen35_xmx_attention_decode_gqa(query, key, value, output, past, query_heads
     g = gate.view(1, query_heads, head_dim) if gate is not None else None
     sdpa_decode(q, key[: past + 1], value[: past + 1], scale=scale, kv_len=past + 1, gate=g, out=o)
     return output
+
+
+def exchange_bytes(world: int, batch: int, nq: int, hd: int) -> int:
+    """Size of one rank's peer-exchange buffer for sequence-sharded decode."""
+    return int(_lib.load().arc_sdpa_exchange_bytes(world, batch, nq, hd))
 
 
 def device_status(device=None) -> tuple[int, int]:

@@ -114,26 +114,64 @@ class SeqShardedDecode:
     """Sequence-sharded decode step with persistent exchange buffers.
 
     Each rank holds keys [begin, end) of every sequence (``k_local``/``v_local``:
-    (B, local_len, nkv, hd)) and the full query.  ``__call__`` enqueues, on the
-    current stream: local split-KV decode writing straight into the send record,
-    one all-gather, one merge.
+    (B, local_len, nkv, hd)) and the full query.  Two exchange paths:
+
+    * ``peer`` (default when symmetric memory can be set up): two launches per step.  The decode
+      merge kernel stores this rank's ``(out, lse)`` records straight into every rank's exchange
+      buffer over NVLink, raises a per-row flag there, waits (bounded) for all ranks' flags for
+      its rows and folds the records — the exchange is part of the kernel, no collective call.
+    * ``nccl``: local decode writes the packed record, one ``all_gather_into_tensor`` moves it,
+      the uniform merge kernel folds the gathered records in place.
     """
 
-    def __init__(self, batch: int, nq: int, hd: int, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, batch: int, nq: int, hd: int, device: torch.device, group: Optional[dist.ProcessGroup] = None,
+                 exchange: str = "auto"):
         from . import ops  # GPU-only import
         self._ops = ops
         self.batch, self.nq, self.hd = batch, nq, hd
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        n = record_numel(batch, nq, hd)
-        self.record = torch.empty(n, dtype=torch.float32, device=device)
-        self.gathered = torch.empty((self.world, n), dtype=torch.float32, device=device)
-        self.part_out, self.part_lse = split_record(self.record, batch, nq, hd)
-        self.all_out, self.all_lse = split_record(self.gathered, batch, nq, hd)
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.out = torch.empty((batch, nq, hd), dtype=torch.bfloat16, device=device)
+        self.step = 0
+        self.mode = "local" if self.world == 1 else exchange
+        self.peer_error: Optional[str] = None
+        if self.mode in ("auto", "peer"):
+            try:
+                self._setup_peer(device)
+                self.mode = "peer"
+            except Exception as e:  # symmetric memory unavailable: fall back to the collective
+                if exchange == "peer":
+                    raise
+                self.peer_error = repr(e)
+                self.mode = "nccl"
+        if self.mode in ("nccl", "local"):
+            n = record_numel(batch, nq, hd)
+            self.record = torch.empty(n, dtype=torch.float32, device=device)
+            self.gathered = torch.empty((self.world, n), dtype=torch.float32, device=device)
+            self.part_out, self.part_lse = split_record(self.record, batch, nq, hd)
+            self.all_out, self.all_lse = split_record(self.gathered, batch, nq, hd)
+
+    def _setup_peer(self, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        nbytes = self._ops.exchange_bytes(self.world, self.batch, self.nq, self.hd)
+        self._xbuf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self._xbuf.zero_()
+        grp = self.group if self.group is not None else dist.group.WORLD
+        self._xhdl = symm_mem.rendezvous(self._xbuf, grp)
+        ptrs = [int(x) for x in self._xhdl.buffer_ptrs]
+        if len(ptrs) != self.world:
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected number of peers")
+        self._peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anyone stores to them
 
     def __call__(self, q, k_local, v_local, *, scale, kv_len=None, gate=None):
         ops = self._ops
+        if self.mode == "peer":
+            self.step += 1
+            return ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, gate=gate, out=self.out,
+                                   exchange=(self._peers, self.world, self.rank, self.step))
         ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, return_partial=True, want_out=False,
                         partial_out=self.part_out, partial_lse=self.part_lse)
         if self.world > 1:

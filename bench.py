@@ -405,8 +405,12 @@ class DecodeLong(Workload):
 
     def config(self):
         return {"workload": "config 5: long-context decode, batch 4, 16Q/2KV, hd128, KV 524288 per sequence",
-                "partition": f"KV sequence over {self.world} rank(s) ({self.local} keys each); one all-gather of "
-                             "the packed (out, lse) record per rank, then the LSE merge on every rank",
+                "partition": f"KV sequence over {self.world} rank(s) ({self.local} keys each); (out, lse) records "
+                             f"exchanged by: {self.runner.mode}"
+                             + (" (in-kernel stores into peers' memory over NVLink, flags, merge in the same kernel)"
+                                if self.runner.mode == "peer" else
+                                " (NCCL all-gather of the packed record, then the LSE merge kernel)"
+                                if self.runner.mode == "nccl" else ""),
                 "timing": "KV (2.1 GB whole job) larger than L2, no flush"}
 
 
@@ -621,6 +625,12 @@ def main():
         run_reference_arm(args)
         return
 
+    # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE JSON
+    # line there.  Everything but that line goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
     if not torch.cuda.is_available():
@@ -672,7 +682,8 @@ def main():
             line["cpu_baseline"] = cpu
         if extra:
             line["extra"] = extra
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

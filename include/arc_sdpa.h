@@ -134,7 +134,23 @@ typedef struct arc_sdpa_decode_params {
     int32_t num_ctas; /* 0 -> one per SM */
     void* workspace;
     size_t workspace_bytes;
+    /* Sequence-sharded decode over NVLink peer memory (optional; xchg_world <= 1: off).
+     * Each of xchg_world ranks (one process per GPU) holds a slice of every sequence's keys and
+     * calls this function with the same batch / heads and the same xchg_step, which must grow
+     * by one per call.  xchg_peers: DEVICE array of xchg_world addresses, entry r = base of rank
+     * r's exchange buffer of arc_sdpa_exchange_bytes() bytes, mapped into this process (peer
+     * access / symmetric memory), zero-filled before the first step.  The merge kernel stores
+     * this rank's (out, lse) records into every rank's buffer, then waits — bounded, about a
+     * second, after which ARC_ERR_DEVICE_WAIT_TIMEOUT shows in arc_sdpa_device_status() — for
+     * all ranks' records and writes the merged (and gated) result to `out`.  `out_f32` /
+     * `out_lse`, if given, still receive this rank's own partial. */
+    const uint64_t* xchg_peers;
+    int32_t xchg_world, xchg_rank;
+    uint32_t xchg_step;
 } arc_sdpa_decode_params;
+
+/* Bytes of one rank's exchange buffer for sequence-sharded decode. */
+size_t arc_sdpa_exchange_bytes(int32_t world, int32_t batch, int32_t nq, int32_t hd);
 
 size_t arc_sdpa_decode_workspace_bytes(const arc_sdpa_decode_params* p);
 int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream);
