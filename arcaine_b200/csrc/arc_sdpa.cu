@@ -87,8 +87,10 @@ static int device_state(DeviceState** out) {
                 }
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128>, PrefillCfg<128>::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, true>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, true>, PrefillCfg<256>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 1>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
@@ -217,7 +219,11 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     if (total_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
     kp.total_tiles = (int)total_tiles;
     const unsigned ctas = (unsigned)(total_tiles < ds->sm_count ? total_tiles : ds->sm_count);
-    sdpa_prefill_kernel<HD><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+    // The additive-mask form is a kernel of its own: the common one stays small.
+    if (kp.mask_type == 1 && kp.mask != nullptr)
+        sdpa_prefill_kernel<HD, true><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+    else
+        sdpa_prefill_kernel<HD, false><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
 

@@ -276,7 +276,7 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
     return t;
 }
 
-template <int HD>
+template <int HD, bool ADD_MASK>
 __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -504,7 +504,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         const uint32_t tS0 = tmem_base + lane_sel + C::COL_S + kh * 64;
         const uint32_t tO = tmem_base + lane_sel + C::COL_O + kh * OC;
         const float sl = p.scale_log2;
-        const bool has_mask = (p.mask_type == 1) && p.mask != nullptr;
+        constexpr bool has_mask = ADD_MASK;  // the additive-mask form is a kernel of its own: the common one stays small
 
         int gb = 0, tc = 0;  // key blocks and non-empty tiles processed so far
         bool ok = true;
