@@ -118,6 +118,29 @@ __device__ __forceinline__ float poly_exp2(float x) {
     return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
+// The same for two values at once on the packed fp32 pipe.
+__device__ __forceinline__ void poly_exp2_x2(uint64_t x, float& r0, float& r1) {
+    float x0, x1;
+    unpack_f32x2(x, x0, x1);
+    x = pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+    const uint64_t t = add_f32x2(x, pack_f32x2(12582912.0f, 12582912.0f));
+    const uint64_t u = add_f32x2(t, pack_f32x2(-12582912.0f, -12582912.0f));
+    const uint64_t f = fma_f32x2(u, pack_f32x2(-1.0f, -1.0f), x);
+    uint64_t p = fma_f32x2(f, pack_f32x2(0.0551716610789299f, 0.0551716610789299f),
+                           pack_f32x2(0.2426111251115799f, 0.2426111251115799f));
+    p = fma_f32x2(f, p, pack_f32x2(0.6932609677314758f, 0.6932609677314758f));
+    p = fma_f32x2(f, p, pack_f32x2(0.9999280571937561f, 0.9999280571937561f));
+    float p0, p1, t0, t1;
+    unpack_f32x2(p, p0, p1);
+    unpack_f32x2(t, t0, t1);
+    r0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+    r1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
+#ifndef ARC_POLY_MOD
+#define ARC_POLY_MOD 8  // one pair of scores in every ARC_POLY_MOD pairs takes the polynomial
+#endif
+
 // Maximum of one 32-column chunk, folded into four independent running maxima.
 template <int MODE>
 __device__ __forceinline__ void chunk_max(const uint32_t (&v)[32], float (&mx)[4], float sl, int key0,
@@ -143,23 +166,45 @@ __device__ __forceinline__ void chunk_max(const uint32_t (&v)[32], float (&mx)[4
 template <int MODE>
 __device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk)[16], float (&ls)[4], float sl,
                                           float m_eff, int key0, const RowMask& rm) {
+    if constexpr (MODE == 0) {
+        // Every key visible: two scores per instruction on the packed fp32 pipe (scale and
+        // subtract the maximum with one fma.f32x2, accumulate the row sum with one add.f32x2),
+        // which leaves the issue port to the exponentials and to the MMA-issuing warp.
+        const uint64_t sl2 = pack_f32x2(sl, sl);
+        const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
+        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-        float p0, p1;
-        if (MODE != 0) {
-            p0 = fast_exp2(masked_score<MODE>(v[e], sl, key0 + e, rm) - m_eff);
-            p1 = fast_exp2(masked_score<MODE>(v[e + 1], sl, key0 + e + 1, rm) - m_eff);
-        } else {
-            // One of every sixteen exponentials is evaluated on the FMA pipe (degree-3 polynomial,
-            // relative error 7.5e-5, far below bf16 resolution).  The softmax is bound almost
-            // equally by the quarter-rate ex2 unit and by instruction issue, so only a small
-            // share can move before issue becomes the limit.
-            p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, -m_eff));
-            p1 = ((e >> 1) & 7) == 5 ? poly_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff))
-                                     : fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, -m_eff));
+        for (int e = 0; e < 32; e += 2) {
+            const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), sl2, nm2);
+            // A share of the exponentials is evaluated on the FMA pipe (degree-3 polynomial,
+            // relative error 7.5e-5, far below bf16 resolution): the quarter-rate ex2 unit is
+            // what bounds this loop.
+            float p0, p1;
+            if (((e >> 1) & (ARC_POLY_MOD - 1)) == 1) {
+                poly_exp2_x2(x, p0, p1);
+            } else {
+                float x0, x1;
+                unpack_f32x2(x, x0, x1);
+                p0 = fast_exp2(x0);
+                p1 = fast_exp2(x1);
+            }
+            acc[(e >> 1) & 3] = add_f32x2(acc[(e >> 1) & 3], pack_f32x2(p0, p1));
+            pk[e >> 1] = pack_bf16x2(p0, p1);
         }
-        ls[(e >> 1) & 3] += p0 + p1;
-        pk[e >> 1] = pack_bf16x2(p0, p1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float a, b;
+            unpack_f32x2(acc[u], a, b);
+            ls[u] += a + b;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+            const float p0 = fast_exp2(masked_score<MODE>(v[e], sl, key0 + e, rm) - m_eff);
+            const float p1 = fast_exp2(masked_score<MODE>(v[e + 1], sl, key0 + e + 1, rm) - m_eff);
+            ls[(e >> 1) & 3] += p0 + p1;
+            pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
     }
 }
 
