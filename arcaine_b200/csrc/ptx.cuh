@@ -226,6 +226,48 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
 }
 
+// Eight MMAs of one K = 128 slab in a single statement: the issuing thread spends eight issue
+// slots instead of eight rounds of address arithmetic, which matters because it shares an
+// instruction scheduler with busy softmax warps.  The first MMA accumulates only if asked to.
+__device__ __forceinline__ void umma_ss_x8(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8],
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %18, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %9, %17, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %17, q;\n\t}" ::"r"(d_tmem),
+        "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]), "l"(b[0]), "l"(b[1]),
+        "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same with the A operand in tensor memory.
+__device__ __forceinline__ void umma_ts_x8(uint32_t d_tmem, const uint32_t (&a)[8], const uint64_t (&b)[8],
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %18, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %9, %17, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %10, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %17, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %17, q;\n\t}" ::"r"(d_tmem),
+        "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "l"(b[0]), "l"(b[1]),
+        "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Warp-uniform forms: every lane executes the statement with identical operands and only the
 // lane whose `leader` flag is set issues the instruction.  Keeping the surrounding address
 // arithmetic uniform across the warp lets it live in the uniform datapath, which matters when
