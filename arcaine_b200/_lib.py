@@ -35,7 +35,7 @@ STATIC_SCRATCH_BYTES = 8 << 20
 EXPORTS = (
     "arc_sdpa_status_string", "arc_sdpa_last_error", "arc_sdpa_prefill_workspace_bytes", "arc_sdpa_prefill",
     "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_exchange_bytes", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
-    "arc_fill_causal_mask", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
+    "arc_fill_causal_mask", "arc_qkv_prepare", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
 )
 
 
@@ -64,6 +64,23 @@ class DecodeParams(C.Structure):
         ("scale", C.c_float), ("num_ctas", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("xchg_peers", C.c_void_p), ("xchg_world", C.c_int32), ("xchg_rank", C.c_int32), ("xchg_step", C.c_uint32),
+    ]
+
+
+class QkvPrepareParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_src", C.c_void_p), ("v_src", C.c_void_p), ("k_dst", C.c_void_p), ("v_dst", C.c_void_p),
+        ("q_weight", C.c_void_p), ("k_weight", C.c_void_p), ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("pos_offset", C.c_void_p),
+        ("batch", C.c_int32), ("seq", C.c_int32), ("nq", C.c_int32), ("nkv", C.c_int32), ("hd", C.c_int32),
+        ("n_active_pairs", C.c_int32),
+        ("q_stride_b", C.c_int64), ("q_stride_t", C.c_int64),
+        ("k_src_stride_b", C.c_int64), ("k_src_stride_t", C.c_int64),
+        ("v_src_stride_b", C.c_int64), ("v_src_stride_t", C.c_int64),
+        ("k_dst_stride_b", C.c_int64), ("k_dst_stride_t", C.c_int64),
+        ("v_dst_stride_b", C.c_int64), ("v_dst_stride_t", C.c_int64),
+        ("rope_stride_b", C.c_int64),
+        ("pos0", C.c_int32), ("theta", C.c_float), ("eps", C.c_float),
     ]
 
 
@@ -103,6 +120,8 @@ def load() -> C.CDLL:
     L.arc_mul_sigmoid_inplace.argtypes = [vp, vp, C.c_int64, vp]
     L.arc_fill_causal_mask.restype = C.c_int
     L.arc_fill_causal_mask.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp]
+    L.arc_qkv_prepare.restype = C.c_int
+    L.arc_qkv_prepare.argtypes = [C.POINTER(QkvPrepareParams), vp]
     L.arc_sdpa_device_status.restype = C.c_int
     L.arc_sdpa_device_status.argtypes = [C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
     L.arc_sdpa_clear_device_status.restype = C.c_int

@@ -16,6 +16,7 @@
 
 #include "decode_sm100.cuh"
 #include "prefill_pair_sm100.cuh"
+#include "qkv_prepare_sm100.cuh"
 #include "prefill_sm100.cuh"
 
 namespace arc {
@@ -585,6 +586,72 @@ extern "C" int arc_mul_sigmoid_inplace(void* a, const void* gate, int64_t n, voi
         static_cast<uint16_t*>(a), static_cast<const uint16_t*>(gate), n);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
+}
+
+extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
+    if (!p) return ARC_ERR_NULL_POINTER;
+    if (p->batch <= 0 || p->seq < 0 || p->nq < 0 || p->nkv < 0) return ARC_ERR_BAD_SHAPE;
+    if (p->hd != 128 && p->hd != 256 && p->hd != 512) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
+    if (p->n_active_pairs < 0 || p->n_active_pairs > p->hd / 2) return ARC_ERR_BAD_SHAPE;
+    if ((p->rope_cos == nullptr) != (p->rope_sin == nullptr)) return ARC_ERR_NULL_POINTER;
+    if (p->n_active_pairs > 0 && !p->rope_cos && !(p->theta > 0.f)) return ARC_ERR_BAD_SHAPE;
+    if (p->k_src && !p->k_dst) return ARC_ERR_NULL_POINTER;
+    if (p->v_dst && !p->v_src && !p->k_src) return ARC_ERR_NULL_POINTER;
+    if (!p->q && !p->k_src && !p->v_dst) return ARC_OK;
+    if (p->seq == 0) return ARC_OK;
+    auto aligned = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
+    if (!aligned(p->q) || !aligned(p->k_src) || !aligned(p->v_src) || !aligned(p->k_dst) || !aligned(p->v_dst) ||
+        !aligned(p->q_weight) || !aligned(p->k_weight))
+        return ARC_ERR_ALIGNMENT;
+    const int64_t strides[] = {p->q_stride_b, p->q_stride_t, p->k_src_stride_b, p->k_src_stride_t, p->v_src_stride_b,
+                               p->v_src_stride_t, p->k_dst_stride_b, p->k_dst_stride_t, p->v_dst_stride_b, p->v_dst_stride_t};
+    for (int64_t st : strides)
+        if (st % 8 != 0) return ARC_ERR_ALIGNMENT;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc != ARC_OK) return rc;
+
+    QkvPrepareParams kp{};
+    kp.q = static_cast<uint16_t*>(p->q);
+    kp.k_src = static_cast<const uint16_t*>(p->k_src);
+    kp.v_src = static_cast<const uint16_t*>(p->v_src);
+    kp.k_dst = static_cast<uint16_t*>(p->k_dst);
+    kp.v_dst = static_cast<uint16_t*>(p->v_dst);
+    kp.q_weight = static_cast<const uint16_t*>(p->q_weight);
+    kp.k_weight = static_cast<const uint16_t*>(p->k_weight);
+    kp.rope_cos = p->rope_cos;
+    kp.rope_sin = p->rope_sin;
+    kp.pos_offset = p->pos_offset;
+    kp.batch = p->batch;
+    kp.seq = p->seq;
+    kp.nq = p->nq;
+    kp.nkv = p->nkv;
+    kp.nap = p->n_active_pairs;
+    kp.q_stride_b = p->q_stride_b;
+    kp.q_stride_t = p->q_stride_t;
+    kp.ks_stride_b = p->k_src_stride_b;
+    kp.ks_stride_t = p->k_src_stride_t;
+    kp.vs_stride_b = p->v_src_stride_b;
+    kp.vs_stride_t = p->v_src_stride_t;
+    kp.kd_stride_b = p->k_dst_stride_b;
+    kp.kd_stride_t = p->k_dst_stride_t;
+    kp.vd_stride_b = p->v_dst_stride_b;
+    kp.vd_stride_t = p->v_dst_stride_t;
+    kp.rope_stride_b = p->rope_stride_b;
+    kp.pos0 = p->pos0;
+    kp.theta = p->theta;
+    kp.eps = p->eps;
+    // One CTA works on one token at a time; eight CTAs per SM keep enough loads in flight.
+    const long long tokens = (long long)p->batch * p->seq;
+    const long long cap = (long long)ds->sm_count * 8;
+    const unsigned ctas = (unsigned)(tokens < cap ? tokens : cap);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (p->hd == 128) qkv_prepare_kernel<2><<<ctas, 256, 0, st>>>(kp);
+    else if (p->hd == 256) qkv_prepare_kernel<4><<<ctas, 256, 0, st>>>(kp);
+    else qkv_prepare_kernel<8><<<ctas, 256, 0, st>>>(kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    ARC_CUDA(cudaGetLastError());
+    return ARC_OK;
 }
 
 extern "C" int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,

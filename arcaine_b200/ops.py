@@ -367,6 +367,95 @@ def qwen35_xmx_attention_decode_gqa(query, key, value, output, past, query_heads
     return output
 
 
+def qkv_prepare(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optional[torch.Tensor], *,
+                k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None, past_len: int = 0,
+                q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                eps: float = 1e-6, theta: float = 10000.0, partial_rotary_factor: float = 1.0,
+                rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                pos_offset=None, v_from_k: bool = False) -> None:
+    """RMSNorm (+ RoPE) of the projected Q / K rows, unit-RMS norm of V and the KV-cache append, one launch.
+
+    q: (B, S, nq, hd) or (S, nq, hd), rewritten in place.  k, v: (B, S, nkv, hd) projections.  K and V go to
+    ``k_cache`` / ``v_cache`` (B, capacity, nkv, hd) at rows ``past_len .. past_len + S`` (no separate copy);
+    without caches K is rewritten in place and V too.  ``v_from_k``: V = unit-RMS norm of the raw K projection
+    (full-attention layers, src/modeling/diffusion_gemma/attention.cpp:587-595).  ``pos_offset``: the position
+    of the first token, an int or a device int32 tensor (B,); defaults to ``past_len``.  With ``rope_cos`` /
+    ``rope_sin`` (S, n_active_pairs) or (B, S, n_active_pairs) f32 the angles are read, otherwise computed.
+    """
+    ref = q if q is not None else k
+    if ref is None:
+        raise ValueError("qkv_prepare needs q or k")
+    three = ref.dim() == 3
+    un = (lambda t: t.unsqueeze(0) if (t is not None and three) else t)
+    q, k, v, k_cache, v_cache = un(q), un(k), un(v), un(k_cache), un(v_cache)
+    ref = q if q is not None else k
+    B, S, _, hd = ref.shape
+    P = _lib.QkvPrepareParams()
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (k_cache, "k_cache"), (v_cache, "v_cache"), (q_weight, "q_weight"),
+                    (k_weight, "k_weight")):
+        if t is not None:
+            _require(t, torch.bfloat16, name)
+    if q is not None:
+        P.q = q.data_ptr()
+        P.nq = q.shape[2]
+        P.q_stride_b, P.q_stride_t = _token_strides(q, "q")
+    if k is not None:
+        P.k_src = k.data_ptr()
+        P.nkv = k.shape[2]
+        P.k_src_stride_b, P.k_src_stride_t = _token_strides(k, "k")
+        kd = k_cache if k_cache is not None else k
+        row0 = past_len if k_cache is not None else 0
+        if k_cache is not None and past_len + S > k_cache.shape[1]:
+            raise ValueError("KV cache capacity exceeded")
+        P.k_dst_stride_b, P.k_dst_stride_t = _token_strides(kd, "k_cache")
+        P.k_dst = kd.data_ptr() + row0 * P.k_dst_stride_t * 2
+        if v is not None or v_from_k:
+            vd = v_cache if v_cache is not None else (v if v is not None else None)
+            if vd is None:
+                raise ValueError("v_from_k needs v_cache")
+            P.v_dst_stride_b, P.v_dst_stride_t = _token_strides(vd, "v_cache")
+            P.v_dst = vd.data_ptr() + (past_len if v_cache is not None else 0) * P.v_dst_stride_t * 2
+            if v is not None and not v_from_k:
+                P.v_src = v.data_ptr()
+                P.v_src_stride_b, P.v_src_stride_t = _token_strides(v, "v")
+    P.q_weight = q_weight.data_ptr() if q_weight is not None else None
+    P.k_weight = k_weight.data_ptr() if k_weight is not None else None
+    P.batch, P.seq, P.hd = B, S, hd
+    P.n_active_pairs = int(partial_rotary_factor * hd / 2.0)
+    if rope_cos is not None:
+        _require(rope_cos, torch.float32, "rope_cos")
+        _require(rope_sin, torch.float32, "rope_sin")
+        if not (rope_cos.is_contiguous() and rope_sin.is_contiguous()):
+            raise ValueError("rope tables must be contiguous")
+        P.rope_cos, P.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+        P.rope_stride_b = S * P.n_active_pairs if rope_cos.dim() == 3 else 0
+    if isinstance(pos_offset, torch.Tensor):
+        _require(pos_offset, torch.int32, "pos_offset")
+        P.pos_offset = pos_offset.data_ptr()
+    else:
+        P.pos0 = past_len if pos_offset is None else int(pos_offset)
+    P.theta, P.eps = float(theta), float(eps)
+    _lib.check(_lib.load().arc_qkv_prepare(C.byref(P), _stream_ptr(ref)), "arc_qkv_prepare")
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """In-place RMSNorm over the last dimension of (rows, H) / (S, heads, H): rms_norm / rms_norm_no_scale,
+    src/common/kernels/rms_norm.hpp:9-56 (weight None = unit scale)."""
+    x3 = x if x.dim() == 3 else x.view(x.shape[0], 1, x.shape[-1])
+    qkv_prepare(x3, None, None, q_weight=weight, eps=eps, partial_rotary_factor=0.0)
+    return x
+
+
+def fused_norm_rope_inplace(x: torch.Tensor, weight: torch.Tensor, offset: int, theta: float, partial: float,
+                            eps: float, rope_cos: Optional[torch.Tensor] = None,
+                            rope_sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fused_norm_rope_inplace(x (seq, nheads, hd), weight, offset, theta, partial, eps, cos, sin):
+    src/modeling/diffusion_gemma/attention_kernels.hpp:99-153."""
+    qkv_prepare(x, None, None, q_weight=weight, eps=eps, theta=theta, partial_rotary_factor=partial,
+                rope_cos=rope_cos, rope_sin=rope_sin, pos_offset=offset)
+    return x
+
+
 def exchange_bytes(world: int, batch: int, nq: int, hd: int) -> int:
     """Size of one rank's peer-exchange buffer for sequence-sharded decode."""
     return int(_lib.load().arc_sdpa_exchange_bytes(world, batch, nq, hd))

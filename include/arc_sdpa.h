@@ -34,7 +34,7 @@ extern "C" {
 #define ARC_OK 0
 #define ARC_ERR_BAD_SHAPE 1            /* non-positive size, nq % nkv != 0, ... */
 #define ARC_ERR_ALIGNMENT 2            /* pointer or stride not 16-byte aligned */
-#define ARC_ERR_UNSUPPORTED_HEAD_DIM 3 /* hd not in {128, 256} */
+#define ARC_ERR_UNSUPPORTED_HEAD_DIM 3 /* hd not in {128, 256} (attention) / {128, 256, 512} (qkv_prepare) */
 #define ARC_ERR_WORKSPACE_TOO_SMALL 4
 #define ARC_ERR_CUDA 5                 /* a CUDA runtime / driver call failed */
 #define ARC_ERR_COLLECTIVE 6           /* reserved for the multi-GPU host layer */
@@ -204,6 +204,54 @@ int arc_mul_sigmoid_inplace(void* a, const void* gate, int64_t n, void* stream);
  * src/common/kernels/attention_mask.hpp:12-38.  mask is (q_len, kv_len) f32. */
 int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,
                          int32_t sliding_window, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Pre-processing of the projected Q / K / V rows and the KV-cache append, one
+ * launch.  Replaces, for one layer call: rms_norm / rms_norm_no_scale
+ * (src/common/kernels/rms_norm.hpp:9-56), fused_norm_rope_inplace and
+ * apply_rope (src/modeling/diffusion_gemma/attention_kernels.hpp:99-153,
+ * attention.cpp:529-610) and the two cache memcpys (attention.cpp:1017-1020;
+ * src/modeling/qwen3_5/operators.hpp:136-140).
+ *
+ * Per (token, head) row of hd bf16 values v:
+ *   y = bf16(v * rsqrt(mean(v^2) + eps) * weight)        (weight NULL: unit scale)
+ *   Q and K rows, pairs p < n_active_pairs:  y[p]        = bf16(y0 c - y1 s)
+ *                                            y[p + hd/2] = bf16(y0 s + y1 c)
+ *   with (c, s) = rope_cos/rope_sin[token * n_active_pairs + p], or, tables NULL,
+ *   cos/sin((pos + token) / theta^(2p/hd)) in fp32.
+ * Q is rewritten in place; K rows go to k_dst, V rows (unit scale, no rotation)
+ * to v_dst — pass the cache address of the first appended position, with the
+ * cache's row stride, and the append costs no copy.  v_src NULL with v_dst set:
+ * V is taken from k_src before its norm (the full-attention layers' shared K/V
+ * projection, attention.cpp:587-595).  q NULL, or k_src NULL, skips that part.
+ * hd in {128, 256, 512}; strides in elements, multiples of 8; all pointers
+ * 16-byte aligned.
+ * ------------------------------------------------------------------------- */
+typedef struct arc_qkv_prepare_params {
+    void* q;              /* (batch, seq, nq, hd) bf16, in place; or NULL */
+    const void* k_src;    /* (batch, seq, nkv, hd) bf16; or NULL */
+    const void* v_src;    /* (batch, seq, nkv, hd) bf16; or NULL */
+    void* k_dst;          /* first destination row of K (cache + past_len * row) */
+    void* v_dst;          /* first destination row of V; or NULL */
+    const void* q_weight; /* [hd] bf16 or NULL */
+    const void* k_weight; /* [hd] bf16 or NULL */
+    const float* rope_cos;    /* (seq, n_active_pairs) f32, or NULL: computed from theta */
+    const float* rope_sin;
+    const int32_t* pos_offset; /* device int32[batch]: position of each sequence's first token; or NULL */
+    int32_t batch, seq, nq, nkv, hd;
+    int32_t n_active_pairs;   /* int(partial_rotary_factor * hd / 2); 0: no rotation */
+    int64_t q_stride_b, q_stride_t;
+    int64_t k_src_stride_b, k_src_stride_t;
+    int64_t v_src_stride_b, v_src_stride_t;
+    int64_t k_dst_stride_b, k_dst_stride_t;
+    int64_t v_dst_stride_b, v_dst_stride_t;
+    int64_t rope_stride_b;    /* elements between two sequences' tables; 0: one table for all */
+    int32_t pos0;             /* position of the first token when pos_offset is NULL */
+    float theta;
+    float eps;
+} arc_qkv_prepare_params;
+
+int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream);
 
 /* Device-side status of the current device: 0, or the code of the first bounded
  * wait that gave up since the last clear.  Synchronises the device. */

@@ -58,6 +58,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_fill_causal_mask.argtypes = [vp, i32, i32, i32, i32]
         L.oracle_mul_sigmoid_inplace.restype = None
         L.oracle_mul_sigmoid_inplace.argtypes = [vp, vp, c.c_size_t]
+        L.oracle_norm_rope.restype = None
+        L.oracle_norm_rope.argtypes = [vp, c.c_longlong, vp, c.c_longlong, vp, i32, i32, i32, i32, i32, f32, f32, vp, vp]
         L.oracle_sdpa_f32.restype = i32
         L.oracle_sdpa_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                       f32, vp, i64, vp, vp, vp]
@@ -123,6 +125,23 @@ def mul_sigmoid_inplace(a: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     gb = _bits(gate)
     lib().oracle_mul_sigmoid_inplace(_ptr(ab), _ptr(gb), ab.size)
     return bits_to_bf16(ab).reshape(a.shape)
+
+
+def norm_rope(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, n_active_pairs: int = 0,
+              offset: int = 0, theta: float = 10000.0, rope_cos: Optional[torch.Tensor] = None,
+              rope_sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm (+ RoPE) of x (tokens, heads, hd) bf16; returns a new bf16 tensor."""
+    tokens, heads, hd = x.shape
+    xb = np.ascontiguousarray(_bits(x)).reshape(-1)
+    out = np.empty_like(xb)
+    wb = _bits(weight) if weight is not None else None
+    cos = np.ascontiguousarray(rope_cos.detach().cpu().numpy(), dtype=np.float32) if rope_cos is not None else None
+    sin = np.ascontiguousarray(rope_sin.detach().cpu().numpy(), dtype=np.float32) if rope_sin is not None else None
+    lib().oracle_norm_rope(_ptr(xb), heads * hd, _ptr(out), heads * hd,
+                           _ptr(wb) if wb is not None else None, tokens, heads, hd, n_active_pairs, offset,
+                           theta, eps,
+                           _ptr(cos) if cos is not None else None, _ptr(sin) if sin is not None else None)
+    return bits_to_bf16(out).reshape(x.shape)
 
 
 def sdpa_f32(q, k, v, *, scale: float, mask_type: int = MASK_NONE, window: int = INT_MAX,

@@ -119,6 +119,57 @@ ORACLE_API void oracle_mul_sigmoid_inplace(uint16_t* a, const uint16_t* gate, si
     }
 }
 
+/* ---- RMSNorm (+ RoPE) of one tensor of (tokens, heads, hd) rows -----------
+ * rms_norm: src/common/kernels/rms_norm.hpp:9-49 (weight NULL = rms_norm_no_scale);
+ * rotation and rounding order: fused_norm_rope_inplace,
+ * src/modeling/diffusion_gemma/attention_kernels.hpp:99-153 — the normalised value is
+ * rounded to bf16, then pairs (p, p + hd/2), p < n_active_pairs, are rotated by the
+ * table entry [token * n_active_pairs + p] or, table NULL, by
+ * angle = (offset + token) / theta^(2p/hd) evaluated in fp32.  The sum of squares is
+ * taken in double here (the reference reduces in fp32 in work-group order): the
+ * result can differ from any fp32 evaluation by one bf16 step in rare elements.
+ * src and dst may alias; strides are in elements between tokens. */
+ORACLE_API void oracle_norm_rope(const uint16_t* src, long long src_stride_t, uint16_t* dst,
+                                 long long dst_stride_t, const uint16_t* weight, int tokens, int heads,
+                                 int hd, int n_active_pairs, int offset, float theta, float eps,
+                                 const float* rope_cos, const float* rope_sin) {
+    const int half = hd / 2;
+    for (int t = 0; t < tokens; ++t) {
+        for (int h = 0; h < heads; ++h) {
+            const uint16_t* x = src + (long long)t * src_stride_t + (long long)h * hd;
+            uint16_t* y = dst + (long long)t * dst_stride_t + (long long)h * hd;
+            double ss = 0.0;
+            for (int d = 0; d < hd; ++d) {
+                double v = b2f(x[d]);
+                ss += v * v;
+            }
+            const float rms_inv = (float)(1.0 / sqrt(ss / (double)hd + (double)eps));
+            float row[1024];
+            for (int d = 0; d < hd; ++d) {
+                float v = b2f(x[d]) * rms_inv;
+                if (weight) v *= b2f(weight[d]);
+                row[d] = b2f(f2b(v));
+            }
+            for (int p = 0; p < n_active_pairs; ++p) {
+                float c, sn;
+                if (rope_cos) {
+                    c = rope_cos[(long long)t * n_active_pairs + p];
+                    sn = rope_sin[(long long)t * n_active_pairs + p];
+                } else {
+                    float inv_freq = 1.0f / powf(theta, 2.0f * (float)p / (float)hd);
+                    float angle = (float)(offset + t) * inv_freq;
+                    c = cosf(angle);
+                    sn = sinf(angle);
+                }
+                const float x0 = row[p], x1 = row[p + half];
+                row[p] = x0 * c - x1 * sn;
+                row[p + half] = x0 * sn + x1 * c;
+            }
+            for (int d = 0; d < hd; ++d) y[d] = f2b(row[d]);
+        }
+    }
+}
+
 /* ---- grading oracle: fp32-softmax SDPA ------------------------------------
  * O = softmax(scale * Q K^T + mask) V on the bf16-valued inputs, with GQA
  * kv_head = q_head / (nq / nkv) (src/common/layers/attention_layout.hpp:37-52,

@@ -42,7 +42,8 @@ def test_struct_layouts_match_the_header():
     """ctypes mirrors of the parameter structs have the field order of the C declarations."""
     from arcaine_b200 import _lib
     text = open(os.path.join(ROOT, "include", "arc_sdpa.h")).read()
-    for cname, cls in (("arc_sdpa_prefill_params", _lib.PrefillParams), ("arc_sdpa_decode_params", _lib.DecodeParams)):
+    for cname, cls in (("arc_sdpa_prefill_params", _lib.PrefillParams), ("arc_sdpa_decode_params", _lib.DecodeParams),
+                       ("arc_qkv_prepare_params", _lib.QkvPrepareParams)):
         body = re.search(r"typedef struct " + cname + r" \{(.*?)\} " + cname + ";", text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -65,6 +66,8 @@ def test_no_cpu_fallback():
         ops.sdpa_prefill(q, q, q, scale=1.0)
     with pytest.raises(ValueError, match="no CPU path"):
         ops.sdpa_decode(q, q, q, scale=1.0)
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.qkv_prepare(q, None, None)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -148,3 +148,49 @@ def test_split_merge_identity():
     merged, lse = oracle.merge_partials(torch.stack(outs), torch.stack(lses))
     assert torch.allclose(merged, whole.reshape(-1, 128), atol=2e-6)
     assert torch.allclose(lse, lse_whole.reshape(-1), atol=2e-6)
+
+
+def _torch_norm_rope(x, w, eps, nap, offset, theta):
+    """RMSNorm then RoPE in plain torch fp32, with the reference's rounding points."""
+    xf = x.float()
+    rms = torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps)
+    n = xf * rms
+    if w is not None:
+        n = n * w.float()
+    n = n.bfloat16().float()
+    hd = x.shape[-1]
+    if nap:
+        p = torch.arange(nap).float()
+        inv = 1.0 / torch.pow(torch.tensor(float(theta)), 2.0 * p / hd)
+        ang = (torch.arange(x.shape[0]).float() + offset)[:, None] * inv[None]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        o = n.clone()
+        o[..., :nap] = n[..., :nap] * c - n[..., hd // 2:hd // 2 + nap] * s
+        o[..., hd // 2:hd // 2 + nap] = n[..., :nap] * s + n[..., hd // 2:hd // 2 + nap] * c
+        n = o
+    return n.bfloat16()
+
+
+@pytest.mark.parametrize("hd,partial", [(128, 1.0), (256, 0.25), (512, 0.0)])
+def test_norm_rope_restatement_matches_torch(hd, partial):
+    """rms_norm + fused_norm_rope_inplace (src/common/kernels/rms_norm.hpp:9-49,
+    src/modeling/diffusion_gemma/attention_kernels.hpp:99-153) against an independent torch formulation:
+    at most one bf16 step apart, and that in very few elements (fp32 vs double sum of squares)."""
+    x = seeded_bf16(9, 3, hd, seed=hd)
+    w = (seeded_bf16(hd, seed=hd + 1).float() * 0.1 + 1.0).bfloat16()
+    nap = int(partial * hd / 2.0)
+    for weight in (w, None):
+        got = oracle.norm_rope(x, weight, eps=1e-6, n_active_pairs=nap, offset=11, theta=10000.0)
+        want = _torch_norm_rope(x, weight, 1e-6, nap, 11, 10000.0)
+        diff = (got.float() - want.float()).abs()
+        step = want.float().abs() * 2.0 ** -7 + 1e-30
+        assert (diff <= step).all()
+        assert (got != want).float().mean() < 5e-3
+    # table mode reads the angles instead of computing them
+    if nap:
+        p = torch.arange(nap).float()
+        inv = 1.0 / torch.pow(torch.tensor(10000.0), 2.0 * p / hd)
+        ang = (torch.arange(9).float() + 11)[:, None] * inv[None]
+        got_t = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, rope_cos=torch.cos(ang), rope_sin=torch.sin(ang))
+        want_t = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, offset=11, theta=10000.0)
+        assert (got_t.float() - want_t.float()).abs().max() <= 2.0 ** -7 * want_t.float().abs().max()

@@ -1,0 +1,65 @@
+"""Parity of the experimental two-tiles-per-CTA prefill kernel (head dim 128) with the CPU oracle.
+
+The kernel is opt-in through ARC_SDPA_PREFILL_KERNEL=pair, read once per process, so the cases run in a
+child process with that variable set.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CHILD = r"""
+import sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + '/tests')
+import torch
+from helpers import assert_close, seeded_bf16
+import oracle
+from arcaine_b200 import ops
+ops.clear_device_status()
+cases = [  # seq, kv_len, nq, nkv, mask_type, window, gate
+    (300, 300, 8, 4, 0, oracle.INT_MAX, False),
+    (300, 300, 8, 4, 3, oracle.INT_MAX, True),
+    (1000, 1000, 4, 2, 3, 100, False),
+    (1, 129, 4, 2, 3, oracle.INT_MAX, False),
+    (129, 127, 4, 2, 3, 64, False),      # kv_len < seq: leading queries see nothing
+    (130, 1000, 4, 2, 3, oracle.INT_MAX, False),
+    (257, 257, 2, 1, 0, oracle.INT_MAX, False),
+    (2048, 2048, 4, 2, 3, 1024, False),
+]
+for i, (seq, kv, nq, nkv, mt, w, gate) in enumerate(cases):
+    q, k, v = seeded_bf16(seq, nq, 128, seed=900 + i), seeded_bf16(kv, nkv, 128, seed=950 + i), seeded_bf16(kv, nkv, 128, seed=990 + i)
+    g = seeded_bf16(seq, nq, 128, seed=930 + i) if gate else None
+    out, lse = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=0.09, mask_type=mt, window=w, num_splits=1,
+                                gate=g.cuda() if gate else None, return_lse=True)
+    want = oracle.sdpa_f32(q, k, v, scale=0.09, mask_type=mt, window=w, gate=g, want_lse=True)
+    assert_close(out, want[0], f"case {i}")
+    finite = torch.isfinite(want[2])
+    assert torch.equal(torch.isfinite(lse.cpu()), finite), f"case {i}: lse finiteness"
+    assert torch.allclose(lse.cpu()[finite], want[2][finite], atol=2e-3), f"case {i}: lse"
+# batch > 1 and many tiles per CTA: against the default kernel's own parity-tested output is not possible in
+# this process, so check sampled rows against the oracle
+B, S, nq, nkv = 2, 4096, 16, 8
+g = torch.Generator(device='cuda').manual_seed(5)
+q = torch.randn(B, S, nq, 128, generator=g, device='cuda').bfloat16()
+k = torch.randn(B, S, nkv, 128, generator=g, device='cuda').bfloat16()
+v = torch.randn(B, S, nkv, 128, generator=g, device='cuda').bfloat16()
+out = ops.sdpa_prefill(q, k, v, scale=128 ** -0.5, mask_type=3, window=1024)
+from helpers import sample_rows
+rows = sample_rows(S, nq, 400, seed=77)
+want, _ = oracle.sdpa_f32(q[1].cpu(), k[1].cpu(), v[1].cpu(), scale=128 ** -0.5, mask_type=3, window=1024, rows=rows)
+assert_close(out[1].reshape(-1, 128)[rows], want, "batch 2 x 4096")
+assert ops.device_status() == (0, 0)
+assert ops.launch_count() > 0
+print("PAIR-OK")
+"""
+
+
+def test_pair_kernel_matches_oracle():
+    env = dict(os.environ, ARC_SDPA_PREFILL_KERNEL="pair")
+    res = subprocess.run([sys.executable, "-c", CHILD, ROOT], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "PAIR-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
