@@ -156,4 +156,74 @@ void fill_causal_mask(cudaStream_t stream, float* mask, int q_len, int kv_len, i
     throw_on(arc_fill_causal_mask(mask, q_len, kv_len, past_offset, sliding_window, stream), "fill_causal_mask");
 }
 
+void rms_norm(cudaStream_t stream, const bf16* x, const bf16* weight, bf16* out, int rows, int H, float eps) {
+    // One "head" per row; out of place is the K path of the kernel (source and destination rows differ).
+    arc_qkv_prepare_params p{};
+    p.batch = 1;
+    p.seq = rows;
+    p.hd = H;
+    p.eps = eps;
+    if (x == out) {
+        p.q = out;
+        p.nq = 1;
+        p.q_stride_t = H;
+        p.q_weight = weight;
+    } else {
+        p.k_src = x;
+        p.k_dst = out;
+        p.nkv = 1;
+        p.k_src_stride_t = p.k_dst_stride_t = H;
+        p.k_weight = weight;
+    }
+    throw_on(arc_qkv_prepare(&p, stream), "rms_norm");
+}
+
+void fused_norm_rope_inplace(cudaStream_t stream, bf16* x, const bf16* weight, int seq, int nheads, int hd,
+                             int offset, float theta, float partial, float eps, const float* rope_cos,
+                             const float* rope_sin) {
+    arc_qkv_prepare_params p{};
+    p.q = x;
+    p.q_weight = weight;
+    p.batch = 1;
+    p.seq = seq;
+    p.nq = nheads;
+    p.hd = hd;
+    p.q_stride_t = (int64_t)nheads * hd;
+    p.n_active_pairs = static_cast<int>(partial * hd / 2.0f);
+    p.rope_cos = rope_cos;
+    p.rope_sin = rope_sin;
+    p.pos0 = offset;
+    p.theta = theta;
+    p.eps = eps;
+    throw_on(arc_qkv_prepare(&p, stream), "fused_norm_rope_inplace");
+}
+
+void qkv_norm_rope_append(cudaStream_t stream, bf16* Q, const bf16* K, const bf16* V, bf16* k_cache, bf16* v_cache,
+                          int seq, int past_len, int nq, int nkv, int hd, const bf16* q_norm, const bf16* k_norm,
+                          float theta, float partial, float eps, const float* rope_cos, const float* rope_sin) {
+    arc_qkv_prepare_params p{};
+    const int64_t row = (int64_t)nkv * hd;
+    p.q = Q;
+    p.k_src = K;
+    p.v_src = V;
+    p.k_dst = k_cache + (int64_t)past_len * row;
+    p.v_dst = v_cache + (int64_t)past_len * row;
+    p.q_weight = q_norm;
+    p.k_weight = k_norm;
+    p.batch = 1;
+    p.seq = seq;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.hd = hd;
+    p.q_stride_t = (int64_t)nq * hd;
+    p.k_src_stride_t = p.v_src_stride_t = p.k_dst_stride_t = p.v_dst_stride_t = row;
+    p.n_active_pairs = static_cast<int>(partial * hd / 2.0f);
+    p.rope_cos = rope_cos;
+    p.rope_sin = rope_sin;
+    p.pos0 = past_len;
+    p.theta = theta;
+    p.eps = eps;
+    throw_on(arc_qkv_prepare(&p, stream), "qkv_norm_rope_append");
+}
+
 }  // namespace arcaine

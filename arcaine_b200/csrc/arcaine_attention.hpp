@@ -90,4 +90,21 @@ void mul_sigmoid_inplace(cudaStream_t stream, bf16* a, const bf16* gate, size_t 
 void fill_causal_mask(cudaStream_t stream, float* mask, int q_len, int kv_len, int past_offset,
                       int sliding_window);
 
+// src/common/kernels/rms_norm.hpp:9-56 (weight == nullptr: rms_norm_no_scale).  H in {128, 256, 512}.
+void rms_norm(cudaStream_t stream, const bf16* x, const bf16* weight, bf16* out, int rows, int H, float eps);
+
+// src/modeling/diffusion_gemma/attention_kernels.hpp:99-153.  rope_cos / rope_sin: (seq, n_active_pairs)
+// tables or nullptr (angles computed from theta).
+void fused_norm_rope_inplace(cudaStream_t stream, bf16* x, const bf16* weight, int seq, int nheads, int hd,
+                             int offset, float theta, float partial, float eps, const float* rope_cos,
+                             const float* rope_sin);
+
+// The post-projection half of project_qkv plus the cache append of encoder_attention_forward
+// (src/modeling/diffusion_gemma/attention.cpp:529-610, 1017-1020) in one launch: Q normed and rotated in
+// place, K normed and rotated and V unit-normed straight into cache rows past_len .. past_len + seq of
+// (max_seq, nkv, hd) caches.  v == nullptr: V is taken from the raw K projection (full-attention layers).
+void qkv_norm_rope_append(cudaStream_t stream, bf16* Q, const bf16* K, const bf16* V, bf16* k_cache, bf16* v_cache,
+                          int seq, int past_len, int nq, int nkv, int hd, const bf16* q_norm, const bf16* k_norm,
+                          float theta, float partial, float eps, const float* rope_cos, const float* rope_sin);
+
 }  // namespace arcaine

@@ -141,6 +141,24 @@ def cfg4_lengths():
 # Workloads.  Each holds this rank's device-resident inputs, pinned host copies
 # for the end-to-end arm, and enqueues one pass of the operator per step().
 # ---------------------------------------------------------------------------
+def workload_text(name: str) -> str:
+    """One description per workload, shared by this arm's line and the reference arm's."""
+    if name == "prefill_window":
+        return "config 3: sliding-window prefill, batch 4, 32Q/16KV, hd128, seq 8192, causal window 1024"
+    if name == "canvas":
+        return ("config 2: DiffusionGemma denoising-step attention, 16Q/8KV, hd256, 256-token canvas "
+                "over a 2048-token cached prompt, bidirectional, scale 1.0")
+    if name == "decode_gated":
+        return ("config 4: gated decode, batch 64, 24Q/4KV, hd256, kv_len uniform in [1024, 32768] "
+                f"(seed 4, {int(sum(cfg4_lengths()))} keys), output * sigmoid(gate)")
+    if name == "decode_long":
+        return "config 5: long-context decode, batch 4, 16Q/2KV, hd128, KV 524288 per sequence"
+    if name == "qkv_prepare":
+        return ("pre-processing of config 3: RMSNorm + RoPE (Q, K), unit norm (V), KV-cache append; "
+                "batch 4, seq 8192, 32Q/16KV, hd128, angles computed in the kernel")
+    raise KeyError(name)
+
+
 class Workload:
     name = ""
     metric = ""
@@ -239,7 +257,7 @@ class PrefillWindow(Workload):
 
     def config(self):
         c = CFG3
-        return {"workload": "config 3: sliding-window prefill, batch 4, 32Q/16KV, hd128, seq 8192, causal window 1024",
+        return {"workload": workload_text("prefill_window"),
                 "partition": f"KV heads then sequences over {self.world} rank(s); per rank batch {self.B}, "
                              f"{self.nq}Q/{self.nkv}KV; output stays head-sharded",
                 "timing": self.timing_note()}
@@ -299,8 +317,7 @@ class Canvas(Workload):
         self.hout.copy_(self.out, non_blocking=True)
 
     def config(self):
-        return {"workload": "config 2: DiffusionGemma denoising-step attention, 16Q/8KV, hd256, 256-token canvas "
-                            "over a 2048-token cached prompt, bidirectional, scale 1.0",
+        return {"workload": workload_text("canvas"),
                 "partition": f"KV heads over {self.world} rank(s)",
                 "timing": self.timing_note()}
 
@@ -372,8 +389,7 @@ class DecodeGated(Workload):
         self.hout.copy_(self.out, non_blocking=True)
 
     def config(self):
-        return {"workload": "config 4: gated decode, batch 64, 24Q/4KV, hd256, kv_len uniform in [1024, 32768] "
-                            f"(seed 4, {self.total_all} keys), output * sigmoid(gate)",
+        return {"workload": workload_text("decode_gated"),
                 "partition": f"sequences over {self.world} rank(s)",
                 "timing": self.timing_note()}
 
@@ -430,7 +446,7 @@ class DecodeLong(Workload):
         self.hout.copy_(self.runner.out, non_blocking=True)
 
     def config(self):
-        return {"workload": "config 5: long-context decode, batch 4, 16Q/2KV, hd128, KV 524288 per sequence",
+        return {"workload": workload_text("decode_long"),
                 "partition": f"KV sequence over {self.world} rank(s) ({self.local} keys each); (out, lse) records "
                              f"exchanged by: {self.runner.mode}"
                              + (" (in-kernel stores into peers' memory over NVLink, flags, merge in the same kernel)"
@@ -440,7 +456,70 @@ class DecodeLong(Workload):
                 "timing": self.timing_note()}
 
 
-WORKLOADS = {w.name: w for w in (PrefillWindow, Canvas, DecodeGated, DecodeLong)}
+class QkvPrepare(Workload):
+    """The step before config 3's attention: RMSNorm + RoPE of Q and K, unit norm of V, K/V appended to the
+    cache, one launch; tokens dealt to ranks by KV head and sequence like the attention itself."""
+    name = "qkv_prepare"
+    metric = "qkv_prepare_gbs"
+    unit = "GB/s"
+    bound = "hbm"
+
+    def __init__(self, rank, world, device, pin=True):
+        import torch
+        from arcaine_b200 import ops, sharded
+        self.ops, self.torch = ops, torch
+        c = CFG3
+        self.world = world
+        sh = sharded.plan_head_shards(c["nq"], c["nkv"], c["B"], world)[rank]
+        self.B = sh.batch_end - sh.batch_begin
+        self.nq = sh.q_head_end - sh.q_head_begin
+        self.nkv = sh.kv_head_end - sh.kv_head_begin
+        S, hd = c["S"], c["hd"]
+        seed = 7000 + rank
+        self.q = _randn_bf16((self.B, S, self.nq, hd), seed, device)
+        self.k = _randn_bf16((self.B, S, self.nkv, hd), seed + 100, device)
+        self.v = _randn_bf16((self.B, S, self.nkv, hd), seed + 200, device)
+        self.kc = torch.empty_like(self.k)
+        self.vc = torch.empty_like(self.v)
+        self.qw = (_randn_bf16((hd,), seed + 300, device).float() * 0.1 + 1.0).bfloat16()
+        self.kw = (_randn_bf16((hd,), seed + 400, device).float() * 0.1 + 1.0).bfloat16()
+        if pin:
+            self.hq, self.hk, self.hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
+            self.hout = torch.empty(self.q.shape, dtype=self.q.dtype).pin_memory()
+        self.h2d = (self.q.numel() + self.k.numel() + self.v.numel()) * 2
+        self.d2h = self.q.numel() * 2
+
+    def _bytes(self, B, nq, nkv):  # every element read once and written once
+        return 2.0 * B * CFG3["S"] * (nq + 2 * nkv) * CFG3["hd"] * 2
+
+    def working_set_bytes(self):
+        return int(self._bytes(self.B, self.nq, self.nkv))
+
+    def units_total(self):
+        return self._bytes(CFG3["B"], CFG3["nq"], CFG3["nkv"]) / 1e9
+
+    def units_rank(self):
+        return self._bytes(self.B, self.nq, self.nkv) / 1e9
+
+    def step(self):
+        self.ops.qkv_prepare(self.q, self.k, self.v, k_cache=self.kc, v_cache=self.vc, past_len=0,
+                             q_weight=self.qw, k_weight=self.kw, eps=1e-6, theta=10000.0, partial_rotary_factor=1.0)
+
+    def step_e2e(self):
+        self.q.copy_(self.hq, non_blocking=True)
+        self.k.copy_(self.hk, non_blocking=True)
+        self.v.copy_(self.hv, non_blocking=True)
+        self.step()
+        self.hout.copy_(self.q, non_blocking=True)
+
+    def config(self):
+        return {"workload": workload_text("qkv_prepare"),
+                "partition": f"KV heads then sequences over {self.world} rank(s); per rank batch {self.B}, "
+                             f"{self.nq}Q/{self.nkv}KV",
+                "timing": self.timing_note()}
+
+
+WORKLOADS = {w.name: w for w in (PrefillWindow, Canvas, DecodeGated, DecodeLong, QkvPrepare)}
 
 
 # ---------------------------------------------------------------------------
@@ -583,6 +662,22 @@ def cpu_sample(workload: str, reps: int = 1):
             oracle.gqa_attention(q, k, v, **kw)
         dt = (time.perf_counter() - t0) / reps
         return flops / dt / 1e12, "TFLOP/s", cores, sample, dt
+    if workload == "qkv_prepare":
+        c = CFG3
+        S, nq, nkv, hd = 1024, c["nq"], c["nkv"], c["hd"]
+        sample = "1 of 4 sequences, 1024 of 8192 tokens, all heads (single thread: the restatement is scalar)"
+        g = torch.Generator().manual_seed(9)
+        q = torch.randn(S, nq, hd, generator=g).bfloat16()
+        k = torch.randn(S, nkv, hd, generator=g).bfloat16()
+        v = torch.randn(S, nkv, hd, generator=g).bfloat16()
+        w = torch.ones(hd).bfloat16()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            oracle.norm_rope(q, w, eps=1e-6, n_active_pairs=hd // 2, theta=10000.0)
+            oracle.norm_rope(k, w, eps=1e-6, n_active_pairs=hd // 2, theta=10000.0)
+            oracle.norm_rope(v, None, eps=1e-6)
+        dt = (time.perf_counter() - t0) / reps
+        return 2.0 * S * (nq + 2 * nkv) * hd * 2 / dt / 1e9, "GB/s", 1, sample, dt
     # decode: the scalar online-softmax kernel's arithmetic over a slice of the KV
     if workload == "decode_gated":
         c = CFG4
@@ -626,7 +721,8 @@ def run_reference_arm(args):
         "impl": "reference", "metric": cls.metric, "value": round(value, 6), "unit": unit, "n_gpus": args.gpus,
         "steps": steps_done, "warmup": min(args.warmup, 1), "ms_per_step": round(ms, 3), "higher_is_better": True,
         "scaling": cls.scaling, "vs_baseline": None, "dtype": "bf16 storage, fp32 math", "data": "synthetic",
-        "config": {"workload": args.workload, "note": "each step is a bounded sample of the workload on the host CPU"},
+        "config": {"workload": workload_text(args.workload),
+                   "note": "each step is a bounded sample of the workload on the host CPU: " + sample},
         "cpu_baseline": {"value": round(value, 6), "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 6), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -678,7 +774,7 @@ def main():
                        with_e2e=not args.no_e2e)
     extra = {}
     if not args.no_extra:
-        for name in ("decode_gated", "decode_long", "canvas", "prefill_window"):
+        for name in ("decode_gated", "decode_long", "canvas", "qkv_prepare", "prefill_window"):
             if name == args.workload:
                 continue
             try:
