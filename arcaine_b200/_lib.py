@@ -35,7 +35,7 @@ STATIC_SCRATCH_BYTES = 8 << 20
 EXPORTS = (
     "arc_sdpa_status_string", "arc_sdpa_last_error", "arc_sdpa_prefill_workspace_bytes", "arc_sdpa_prefill",
     "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_exchange_bytes", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
-    "arc_fill_causal_mask", "arc_qkv_prepare", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
+    "arc_fill_causal_mask", "arc_fill_causal_mask_with_block_ids", "arc_qkv_prepare", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
 )
 
 
@@ -120,6 +120,8 @@ def load() -> C.CDLL:
     L.arc_mul_sigmoid_inplace.argtypes = [vp, vp, C.c_int64, vp]
     L.arc_fill_causal_mask.restype = C.c_int
     L.arc_fill_causal_mask.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp]
+    L.arc_fill_causal_mask_with_block_ids.restype = C.c_int
+    L.arc_fill_causal_mask_with_block_ids.argtypes = [vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp]
     L.arc_qkv_prepare.restype = C.c_int
     L.arc_qkv_prepare.argtypes = [C.POINTER(QkvPrepareParams), vp]
     L.arc_sdpa_device_status.restype = C.c_int

@@ -646,24 +646,40 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     const long long cap = (long long)ds->sm_count * 8;
     const unsigned ctas = (unsigned)(tokens < cap ? tokens : cap);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (p->hd == 128) qkv_prepare_kernel<2><<<ctas, 256, 0, st>>>(kp);
-    else if (p->hd == 256) qkv_prepare_kernel<4><<<ctas, 256, 0, st>>>(kp);
-    else qkv_prepare_kernel<8><<<ctas, 256, 0, st>>>(kp);
+    if (p->hd == 128) qkv_prepare_kernel<128><<<ctas, 256, 0, st>>>(kp);
+    else if (p->hd == 256) qkv_prepare_kernel<256><<<ctas, 256, 0, st>>>(kp);
+    else qkv_prepare_kernel<512><<<ctas, 256, 0, st>>>(kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
     return ARC_OK;
 }
 
+static int fill_mask(float* mask, const int32_t* block_ids, int32_t q_len, int32_t kv_len, int32_t past_offset,
+                     int32_t sliding_window, void* stream);
+
 extern "C" int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,
                                     int32_t sliding_window, void* stream) {
+    return fill_mask(mask, nullptr, q_len, kv_len, past_offset, sliding_window, stream);
+}
+
+extern "C" int arc_fill_causal_mask_with_block_ids(float* mask, const int32_t* block_ids, int32_t q_len,
+                                                   int32_t kv_len, int32_t past_offset, int32_t sliding_window,
+                                                   void* stream) {
+    // Positions past_offset - (kv_len - q_len) .. past_offset + q_len - 1 are looked up.
+    if (block_ids && past_offset - (kv_len - q_len) < 0) return ARC_ERR_BAD_SHAPE;
+    return fill_mask(mask, block_ids, q_len, kv_len, past_offset, sliding_window, stream);
+}
+
+static int fill_mask(float* mask, const int32_t* block_ids, int32_t q_len, int32_t kv_len, int32_t past_offset,
+                     int32_t sliding_window, void* stream) {
     if (!mask) return ARC_ERR_NULL_POINTER;
     if (q_len < 0 || kv_len < 0) return ARC_ERR_BAD_SHAPE;
     const long long n = (long long)q_len * kv_len;
     if (n == 0) return ARC_OK;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    fill_causal_mask_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(mask, q_len, kv_len,
-                                                                                            past_offset, sliding_window);
+    fill_causal_mask_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        mask, block_ids, q_len, kv_len, past_offset, sliding_window);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
 }

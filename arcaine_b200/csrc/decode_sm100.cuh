@@ -633,15 +633,23 @@ __global__ void mul_sigmoid_kernel(uint16_t* a, const uint16_t* gate, long long 
     }
 }
 
-// Additive causal / sliding-window mask : src/common/kernels/attention_mask.hpp:12-38
-__global__ void fill_causal_mask_kernel(float* mask, int q_len, int kv_len, int past_offset, int window) {
+// Additive causal / sliding-window mask : src/common/kernels/attention_mask.hpp:12-38; with
+// block_ids (one int per absolute position, -1 = text) tokens of the same non-negative block also
+// see each other's future: fill_causal_mask_with_block_ids, attention_mask.hpp:44-73.
+__global__ void fill_causal_mask_kernel(float* mask, const int* block_ids, int q_len, int kv_len, int past_offset,
+                                        int window) {
     const long long n = (long long)q_len * kv_len;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const int qi = (int)(i / kv_len), kvj = (int)(i % kv_len);
         const int q_global = past_offset + qi;
         const int kv_global = past_offset - (kv_len - q_len) + kvj;
-        const bool causal = kv_global > q_global;
+        bool same_block = false;
+        if (block_ids) {
+            const int qb = block_ids[q_global];
+            same_block = qb >= 0 && kv_global >= 0 && qb == block_ids[kv_global];
+        }
+        const bool causal = !same_block && kv_global > q_global;
         const bool too_far = (window != 0x7fffffff) && (kv_global < q_global - window + 1);
         mask[i] = (causal || too_far) ? -CUDART_INF_F : 0.0f;
     }

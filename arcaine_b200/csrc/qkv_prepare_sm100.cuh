@@ -15,8 +15,9 @@
 //
 // Mapping: one CTA per token at a time (grid-stride), cos / sin of the token staged once in
 // shared memory and shared by all its heads (the reference's "Fused" mode), one warp per
-// (token, head) row, each lane holding hd/64 elements of the row's first half and the matching
-// elements of the second half, so a rotation pair never leaves the lane.
+// (token, head) row segment: a lane holds eight consecutive elements of the row's first half and
+// the matching eight of the second half (16-byte loads), so a rotation pair never leaves the lane
+// and a warp covers 4 / 2 / 1 rows at once for head dim 128 / 256 / 512.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -45,55 +46,54 @@ struct QkvPrepareParams {
     float theta, eps;
 };
 
-template <int E> struct RowVec;  // E consecutive bf16
-template <> struct RowVec<2> { using type = uint32_t; };
-template <> struct RowVec<4> { using type = uint2; };
-template <> struct RowVec<8> { using type = uint4; };
-
-template <int E>
-__device__ __forceinline__ void unpack_row(const typename RowVec<E>::type& raw, float (&f)[E]) {
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int i = 0; i < E / 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
         f[2 * i] = __uint_as_float(w[i] << 16);
         f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
 }
 
-template <int E>
-__device__ __forceinline__ typename RowVec<E>::type pack_row(const float (&f)[E]) {
-    typename RowVec<E>::type raw;
-    uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
-#pragma unroll
-    for (int i = 0; i < E / 2; ++i) w[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
-    return raw;
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
 }
 
 __device__ __forceinline__ float bf16_rne(float x) {
     return __uint_as_float(static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x))) << 16);
 }
 
-// HD = 64 * E.  256 threads: 8 warps, each takes rows (heads of Q, then K, then V) of the token.
-template <int E>
+// 256 threads = 8 warps.  A row of HD values is held by HD/16 lanes, each with eight consecutive
+// values of the row's first half and the matching eight of the second half (two 16-byte loads),
+// so a warp works on 32 / (HD/16) rows at once: 4 (HD 128), 2 (HD 256) or 1 (HD 512).
+template <int HD>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams p) {
-    constexpr int HD = 64 * E;
-    __shared__ float s_cos[HD / 2];
-    __shared__ float s_sin[HD / 2];
-    using Vec = typename RowVec<E>::type;
+    constexpr int LPR = HD / 16;    // lanes per row
+    constexpr int RPW = 32 / LPR;   // rows per warp and pass
+    __shared__ float s_cos2[2][HD / 2];  // double-buffered: one barrier per token is enough
+    __shared__ float s_sin2[2][HD / 2];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int sub = lane / LPR;     // which of the warp's rows
+    const int li = lane % LPR;      // position inside the row
     const int rows_q = p.q ? p.nq : 0;
     const int rows_k = p.k_src && p.k_dst ? p.nkv : 0;
     const int rows_v = p.v_dst ? p.nkv : 0;
     const int rows = rows_q + rows_k + rows_v;
     const long long tokens = (long long)p.batch * p.seq;
 
-    for (long long tk = blockIdx.x; tk < tokens; tk += gridDim.x) {
+    // HD / 2 <= 256 = blockDim.x: thread pr owns rotation pair pr, whose frequency never changes.
+    const float inv_freq = (threadIdx.x < p.nap && !p.rope_cos)
+                               ? 1.0f / powf(p.theta, 2.0f * threadIdx.x / static_cast<float>(HD)) : 0.f;
+    int it = 0;
+    for (long long tk = blockIdx.x; tk < tokens; tk += gridDim.x, ++it) {
         const int b = static_cast<int>(tk / p.seq);
         const int t = static_cast<int>(tk - (long long)b * p.seq);
+        float* s_cos = s_cos2[it & 1];
+        float* s_sin = s_sin2[it & 1];
         if (p.nap > 0) {
-            __syncthreads();  // the previous token's readers are done
-            for (int pr = threadIdx.x; pr < p.nap; pr += blockDim.x) {
+            const int pr = threadIdx.x;
+            if (pr < p.nap) {
                 float c, s;
                 if (p.rope_cos) {
                     const long long ti = (long long)b * p.rope_stride_b + (long long)t * p.nap + pr;
@@ -101,21 +101,22 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     s = p.rope_sin[ti];
                 } else {
                     const int pos = (p.pos_offset ? p.pos_offset[b] : p.pos0) + t;
-                    const float inv_freq = 1.0f / powf(p.theta, 2.0f * pr / static_cast<float>(HD));
-                    const float angle = static_cast<float>(pos) * inv_freq;
-                    c = cosf(angle);
-                    s = sinf(angle);
+                    sincosf(static_cast<float>(pos) * inv_freq, &s, &c);
                 }
                 s_cos[pr] = c;
                 s_sin[pr] = s;
             }
+            // Writers of this buffer two tokens ago were read before every thread reached the
+            // previous token's barrier, so one barrier per token orders both directions.
             __syncthreads();
         }
-        for (int r = warp; r < rows; r += 8) {
-            const uint16_t* src;
-            uint16_t* dst;
-            const uint16_t* weight;
-            bool rope;
+        for (int r0 = warp * RPW; r0 < rows; r0 += 8 * RPW) {
+            const int r = r0 + sub;
+            const bool valid = r < rows;
+            const uint16_t* src = nullptr;
+            uint16_t* dst = nullptr;
+            const uint16_t* weight = nullptr;
+            bool rope = false;
             if (r < rows_q) {
                 src = dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
                 weight = p.q_weight;
@@ -126,43 +127,46 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                 dst = p.k_dst + b * p.kd_stride_b + t * p.kd_stride_t + (long long)h * HD;
                 weight = p.k_weight;
                 rope = true;
-            } else {
+            } else if (valid) {
                 const int h = r - rows_q - rows_k;
                 src = p.v_src ? p.v_src + b * p.vs_stride_b + t * p.vs_stride_t + (long long)h * HD
                               : p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
                 dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
-                weight = nullptr;
-                rope = false;
             }
-            float lo[E], hi[E];
-            unpack_row<E>(*reinterpret_cast<const Vec*>(src + lane * E), lo);
-            unpack_row<E>(*reinterpret_cast<const Vec*>(src + HD / 2 + lane * E), hi);
+            float lo[8], hi[8];
+            uint4 rl = make_uint4(0u, 0u, 0u, 0u), rh = rl;
+            if (valid) {
+                rl = *reinterpret_cast<const uint4*>(src + li * 8);
+                rh = *reinterpret_cast<const uint4*>(src + HD / 2 + li * 8);
+            }
+            unpack8(rl, lo);
+            unpack8(rh, hi);
             float ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < E; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+            for (int e = 0; e < 8; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float rms_inv = rsqrtf(ss / static_cast<float>(HD) + p.eps);
             if (weight) {
-                float wl[E], wh[E];
-                unpack_row<E>(*reinterpret_cast<const Vec*>(weight + lane * E), wl);
-                unpack_row<E>(*reinterpret_cast<const Vec*>(weight + HD / 2 + lane * E), wh);
+                float wl[8], wh[8];
+                unpack8(*reinterpret_cast<const uint4*>(weight + li * 8), wl);
+                unpack8(*reinterpret_cast<const uint4*>(weight + HD / 2 + li * 8), wh);
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
+                for (int e = 0; e < 8; ++e) {
                     lo[e] = bf16_rne(lo[e] * rms_inv * wl[e]);
                     hi[e] = bf16_rne(hi[e] * rms_inv * wh[e]);
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
+                for (int e = 0; e < 8; ++e) {
                     lo[e] = bf16_rne(lo[e] * rms_inv);
                     hi[e] = bf16_rne(hi[e] * rms_inv);
                 }
             }
             if (rope) {
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    const int pr = lane * E + e;
+                for (int e = 0; e < 8; ++e) {
+                    const int pr = li * 8 + e;
                     if (pr < p.nap) {
                         const float c = s_cos[pr], s = s_sin[pr];
                         const float x0 = lo[e], x1 = hi[e];
@@ -171,8 +175,10 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     }
                 }
             }
-            *reinterpret_cast<Vec*>(dst + lane * E) = pack_row<E>(lo);
-            *reinterpret_cast<Vec*>(dst + HD / 2 + lane * E) = pack_row<E>(hi);
+            if (valid) {
+                *reinterpret_cast<uint4*>(dst + li * 8) = pack8(lo);
+                *reinterpret_cast<uint4*>(dst + HD / 2 + li * 8) = pack8(hi);
+            }
         }
     }
 }

@@ -305,6 +305,25 @@ def fill_causal_mask(q_len: int, kv_len: int, past_offset: int, sliding_window: 
     return out
 
 
+def fill_causal_mask_with_block_ids(block_ids: Optional[torch.Tensor], q_len: int, kv_len: int, past_offset: int,
+                                    sliding_window: int = NO_WINDOW, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal / sliding-window mask with Gemma4's bidirectional vision blocks
+    (src/common/kernels/attention_mask.hpp:44-73).  block_ids: device int32, one per absolute position."""
+    device = block_ids.device if block_ids is not None else (out.device if out is not None else "cuda")
+    if out is None:
+        out = torch.empty((q_len, kv_len), dtype=torch.float32, device=device)
+    _require(out, torch.float32, "out")
+    if block_ids is not None:
+        _require(block_ids, torch.int32, "block_ids")
+        if block_ids.numel() < past_offset + q_len:
+            raise ValueError("block_ids must cover every position up to past_offset + q_len")
+    with torch.cuda.device(out.device):
+        check(_lib.load().arc_fill_causal_mask_with_block_ids(
+            out.data_ptr(), block_ids.data_ptr() if block_ids is not None else None, q_len, kv_len, past_offset,
+            sliding_window, _stream_ptr(out)), "arc_fill_causal_mask_with_block_ids")
+    return out
+
+
 # ---------------------------------------------------------------------------
 # Reference-named entry points (one sequence, token-major tensors)
 # ---------------------------------------------------------------------------

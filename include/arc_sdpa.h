@@ -205,6 +205,14 @@ int arc_mul_sigmoid_inplace(void* a, const void* gate, int64_t n, void* stream);
 int arc_fill_causal_mask(float* mask, int32_t q_len, int32_t kv_len, int32_t past_offset,
                          int32_t sliding_window, void* stream);
 
+/* The same plus Gemma4's bidirectional vision blocks: fill_causal_mask_with_block_ids,
+ * src/common/kernels/attention_mask.hpp:44-73.  block_ids is a device int32 array
+ * indexed by absolute position (-1 = text token); tokens with the same
+ * non-negative id see each other in both directions.  NULL = plain causal.
+ * Pass the result to arc_sdpa_prefill with mask_type 1. */
+int arc_fill_causal_mask_with_block_ids(float* mask, const int32_t* block_ids, int32_t q_len, int32_t kv_len,
+                                        int32_t past_offset, int32_t sliding_window, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Pre-processing of the projected Q / K / V rows and the KV-cache append, one
  * launch.  Replaces, for one layer call: rms_norm / rms_norm_no_scale

@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_lcg_fill.argtypes = [vp, c.c_size_t, c.POINTER(c.c_uint32)]
         L.oracle_fill_causal_mask.restype = None
         L.oracle_fill_causal_mask.argtypes = [vp, i32, i32, i32, i32]
+        L.oracle_fill_causal_mask_with_block_ids.restype = None
+        L.oracle_fill_causal_mask_with_block_ids.argtypes = [vp, vp, i32, i32, i32, i32]
         L.oracle_mul_sigmoid_inplace.restype = None
         L.oracle_mul_sigmoid_inplace.argtypes = [vp, vp, c.c_size_t]
         L.oracle_norm_rope.restype = None
@@ -117,6 +119,14 @@ def lcg_fill(n: int, state: int) -> tuple[np.ndarray, int]:
 def fill_causal_mask(q_len: int, kv_len: int, past_offset: int, sliding_window: int = INT_MAX) -> np.ndarray:
     m = np.empty((q_len, kv_len), dtype=np.float32)
     lib().oracle_fill_causal_mask(_ptr(m), q_len, kv_len, past_offset, sliding_window)
+    return m
+
+
+def fill_causal_mask_with_block_ids(block_ids, q_len: int, kv_len: int, past_offset: int,
+                                    sliding_window: int = INT_MAX) -> np.ndarray:
+    m = np.empty((q_len, kv_len), dtype=np.float32)
+    ids = None if block_ids is None else np.ascontiguousarray(np.asarray(block_ids), dtype=np.int32)
+    lib().oracle_fill_causal_mask_with_block_ids(_ptr(m), _ptr(ids), q_len, kv_len, past_offset, sliding_window)
     return m
 
 

@@ -87,6 +87,26 @@ ORACLE_API void oracle_fill_causal_mask(float* mask, int q_len, int kv_len,
     }
 }
 
+/* The same with Gemma4's vision blocks: src/common/kernels/attention_mask.hpp:44-73.
+ * block_ids[pos] is -1 for text and a non-negative id per image / video block; tokens
+ * of one block see each other in both directions. */
+ORACLE_API void oracle_fill_causal_mask_with_block_ids(float* mask, const int32_t* block_ids, int q_len,
+                                                       int kv_len, int past_offset, int sliding_window) {
+    for (int qi = 0; qi < q_len; ++qi) {
+        for (int kvj = 0; kvj < kv_len; ++kvj) {
+            int q_global = past_offset + qi;
+            int kv_global = past_offset - (kv_len - q_len) + kvj;
+            int q_block = block_ids ? block_ids[q_global] : -1;
+            int kv_block = block_ids ? block_ids[kv_global] : -1;
+            int same = q_block >= 0 && q_block == kv_block;
+            int causal = !same && kv_global > q_global;
+            int too_far = (sliding_window != INT_MAX) &&
+                          (kv_global < q_global - sliding_window + 1);
+            mask[(size_t)qi * kv_len + kvj] = (causal || too_far) ? -INFINITY : 0.0f;
+        }
+    }
+}
+
 /* Visible key span [lo, hi) of one query row.  mask_type follows the values
  * the reference passes to oneDNN (src/modeling/diffusion_gemma/attention.cpp:
  * 1032,1040,1099): 0 = none, 1 = explicit additive buffer, 3 = causal aligned

@@ -194,3 +194,22 @@ def test_norm_rope_restatement_matches_torch(hd, partial):
         got_t = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, rope_cos=torch.cos(ang), rope_sin=torch.sin(ang))
         want_t = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, offset=11, theta=10000.0)
         assert (got_t.float() - want_t.float()).abs().max() <= 2.0 ** -7 * want_t.float().abs().max()
+
+
+def test_block_id_mask_matches_a_numpy_restatement():
+    """fill_causal_mask_with_block_ids (src/common/kernels/attention_mask.hpp:44-73): causal plus
+    bidirectional attention inside one vision block; no block ids = plain causal mask."""
+    q_len, kv_len, past = 24, 40, 30
+    ids = np.full(past + q_len, -1, dtype=np.int32)
+    ids[20:28] = 0          # a block that straddles the cached part and the new tokens
+    ids[33:41] = 1
+    for window in (oracle.INT_MAX, 12):
+        got = oracle.fill_causal_mask_with_block_ids(ids, q_len, kv_len, past, window)
+        qg = past + np.arange(q_len)[:, None]
+        kg = past - (kv_len - q_len) + np.arange(kv_len)[None, :]
+        same = (ids[qg] >= 0) & (ids[qg] == ids[kg])
+        hidden = (~same & (kg > qg)) | ((window != oracle.INT_MAX) & (kg < qg - window + 1))
+        assert np.array_equal(np.isneginf(got), hidden) and np.all((got == 0) | np.isneginf(got))
+        assert np.array_equal(oracle.fill_causal_mask_with_block_ids(None, q_len, kv_len, past, window),
+                              oracle.fill_causal_mask(q_len, kv_len, past, window))
+    assert np.isfinite(oracle.fill_causal_mask_with_block_ids(ids, q_len, kv_len, past)[4, 23])  # q=34 sees k=37

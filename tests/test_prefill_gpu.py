@@ -164,3 +164,23 @@ def test_error_statuses(ops):
     p.q = big.data_ptr() + 2
     assert L.arc_sdpa_prefill(C.byref(p), None) == _lib.ARC_ERR_ALIGNMENT
     assert L.arc_sdpa_prefill(None, None) == _lib.ARC_ERR_NULL_POINTER
+
+
+def test_vision_block_mask_buffer_and_attention(ops):
+    """Gemma4 vision blocks: the mask kernel against its restatement (bit for bit), then attention through
+    the explicit-mask path against the oracle with the same buffer."""
+    import numpy as np
+    seq, kv_len, past, nq, nkv, hd = 150, 230, 80, 4, 2, 128
+    ids = np.full(past + seq, -1, dtype=np.int32)
+    ids[70:100] = 0
+    ids[140:200] = 1
+    for window in (oracle.INT_MAX, 64):
+        want_mask = oracle.fill_causal_mask_with_block_ids(ids, seq, kv_len, past, window)
+        mask = ops.fill_causal_mask_with_block_ids(torch.from_numpy(ids).cuda(), seq, kv_len, past, window)
+        assert np.array_equal(mask.cpu().numpy(), want_mask)
+        q, k, v = seeded_bf16(seq, nq, hd, seed=71), seeded_bf16(kv_len, nkv, hd, seed=72), seeded_bf16(kv_len, nkv, hd, seed=73)
+        out = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, mask_type=ops.MASK_EXPLICIT, mask=mask)
+        want = oracle.sdpa_f32(q, k, v, scale=hd ** -0.5, mask_type=1, mask=want_mask)
+        assert_close(out, want[0], f"vision blocks, window {window}")
+    plain = ops.fill_causal_mask_with_block_ids(None, seq, kv_len, past, 64, out=torch.empty(seq, kv_len, device="cuda"))
+    assert torch.equal(plain, ops.fill_causal_mask(seq, kv_len, past, 64))
