@@ -36,8 +36,8 @@ struct PairCfg {
     static constexpr int COL_S = 0;    // + 128 * pipeline
     static constexpr int COL_O = 256;  // + 128 * pipeline
     // q_full[2] q_empty[2] k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] then per pipeline:
-    // s_full p_full pv_done o_full o_empty
-    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 10;
+    // s_full p_full pv_done o_full o_empty turn
+    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 12;
     static constexpr int SMEM_BYTES = (2 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;  // four per pipeline
     static constexpr int PRODUCER_WARP = 8;
@@ -119,6 +119,7 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
     uint64_t* pv_done = p_full + 2;  // one phase per key block: O += P V of that block has completed
     uint64_t* o_full = pv_done + 2;  // one phase per tile
     uint64_t* o_empty = o_full + 2;  // one phase per tile: the softmax warps have read O out
+    uint64_t* turn = o_empty + 2;    // one phase per union key block: the pipeline's softmax warps are past it
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
 
@@ -138,6 +139,7 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
             mbar_init(&pv_done[s], 1);
             mbar_init(&o_full[s], 1);
             mbar_init(&o_empty[s], 128);
+            mbar_init(&turn[s], 128);
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
@@ -341,6 +343,7 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
         const int off = p.kv_len - p.seq;
 
         int g = 0, tq = 0;  // key blocks and tiles (with key blocks) of this pipeline so far
+        int gu = 0;         // union key blocks of the CTA so far (the same count in both pipelines)
         bool ok = true;
         uint32_t wa[32], wb[32];
 #ifdef ARC_PREFILL_TRACE
@@ -357,21 +360,22 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
         TileCursor cur;
         for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
             const PairWork pw = decode_pair(p, cur);
-            if (!pw.live_of(s)) continue;
-            const int t = pw.q0 + s * C::BM + r;
-            const long long row = ((long long)pw.b * p.seq + t) * p.nq + pw.h;
-            const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h * HD;
-            const bool store = t < p.seq;
-            const int lo = pw.lo_of(s), hi = pw.hi_of(s);
-            if (hi == lo) {
-                // Nothing visible: zero output.
-                if (store) {
+            if (pw.uhi == pw.ulo) {
+                // No key block for either tile: zero output for the rows that exist.
+                const int t = pw.q0 + s * C::BM + r;
+                if (pw.live_of(s) && t < p.seq) {
+                    const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h * HD;
                     uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
                     for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
+                    if (p.out_lse) p.out_lse[((long long)pw.b * p.seq + t) * p.nq + pw.h] = -CUDART_INF_F;
                 }
                 continue;
             }
+            const int t = pw.q0 + s * C::BM + r;
+            const long long row = ((long long)pw.b * p.seq + t) * p.nq + pw.h;
+            const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h * HD;
+            const bool store = pw.live_of(s) && t < p.seq;
+            const int lo = pw.lo_of(s), hi = pw.hi_of(s);
             int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
             if (causal) {
                 const int diag = t + off;
@@ -384,87 +388,148 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
             float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
             float l = 0.f;            // row sum
             ARC_TP(1000 + hi - lo);
-            for (int j = lo; j < hi; ++j, ++g) {
+            // Both pipelines walk every key block of the pair, used or not, and take turns at the
+            // exponentials (the two warps of a scheduler share one ex2 unit): A's block u goes after
+            // B's block u - 1, B's block u after A's block u.  That keeps the pipelines half a
+            // period apart, so that one computes while the tensor pipe works for the other.
+            for (int j = pw.ulo; j < pw.uhi; ++j, ++gu) {
+                const bool act = j >= lo && j < hi;
                 const int kc = j * C::BN;
-                ARC_TP(10);
-                if (!mbar_wait_warp(&s_full[s], g & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_S, g);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                ARC_TP(11);
-                // Pass 1: row maximum of the block (chunk c+1 loads while chunk c is reduced).
-                float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                tmem_ld32(tS, wa);
-                tmem_ld32(tS + 32, wb);
-                tmem_wait_ld();
-                chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
-                tmem_ld32(tS + 64, wa);
-                chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
-                tmem_ld32(tS + 96, wb);
-                tmem_wait_ld();
-                chunk_max_any<false>(wa, mr, ms, sl, kc + 64, rm);
-                tmem_ld32(tS, wa);  // first chunk again, for the exponentials
-                chunk_max_any<false>(wb, mr, ms, sl, kc + 96, rm);
-                const float bm = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
-                                       fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
-                const float m_new = fmaxf(m, bm);
-                if (j == lo) {
-                    m = m_new;
-                } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
-                    // Rare: some row's maximum grows by more than 2^8.  Once O += P V of the previous
-                    // block has landed, rescale those rows of O in tensor memory.
-                    const bool need = m_new > m + 8.0f;
-                    const float alpha = !need ? 1.0f : (m_new == -CUDART_INF_F ? 1.0f : fast_exp2(m - m_new));
-                    tmem_wait_ld();
-                    if (!mbar_wait_warp(&pv_done[s], (g - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_O, g);
+                bool full = false;
+                float m_eff = 0.f;
+                if (act) {
+                    ARC_TP(10);
+                    if (!mbar_wait_warp(&s_full[s], g & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_S, g);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-#pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
-                        tmem_ld32(tO + c * 32, wb);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) wb[e] = __float_as_uint(__uint_as_float(wb[e]) * alpha);
-                        tmem_st32(tO + c * 32, wb);
-                    }
-                    tmem_wait_st();
-                    l *= alpha;
-                    if (need) m = m_new;
+                    ARC_TP(11);
+                    // Every key of the block visible to every row of the warp (seven blocks in nine
+                    // with a 1024-key window): no per-element tests and no per-chunk votes.
+                    full = __all_sync(0xffffffffu, rm.lo <= kc && kc + C::BN <= rm.hi);
+                    // Pass 1: row maximum of the block (the next chunk loads while one is reduced).
+                    float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                    float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
                     tmem_ld32(tS, wa);
+                    tmem_ld32(tS + 32, wb);
+                    tmem_wait_ld();
+                    if (full) {
+                        chunk_max<0>(wa, mr, sl, kc, rm);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_max<0>(wb, mr, sl, kc + 32, rm);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_max<0>(wa, mr, sl, kc + 64, rm);
+                        tmem_ld32(tS, wa);  // first chunk again, for the exponentials
+                        chunk_max<0>(wb, mr, sl, kc + 96, rm);
+                    } else {
+                        chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_max_any<false>(wa, mr, ms, sl, kc + 64, rm);
+                        tmem_ld32(tS, wa);
+                        chunk_max_any<false>(wb, mr, ms, sl, kc + 96, rm);
+                    }
+                    const float bm = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                           fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+                    const float m_new = fmaxf(m, bm);
+                    if (j == lo) {
+                        m = m_new;
+                    } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
+                        // Rare: some row's maximum grows by more than 2^8.  Once O += P V of the previous
+                        // block has landed, rescale those rows of O in tensor memory.
+                        const bool need = m_new > m + 8.0f;
+                        const float alpha = !need ? 1.0f : (m_new == -CUDART_INF_F ? 1.0f : fast_exp2(m - m_new));
+                        tmem_wait_ld();
+                        if (!mbar_wait_warp(&pv_done[s], (g - 1) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_O, g);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+#pragma unroll 1
+                        for (int c = 0; c < HD / 32; ++c) {
+                            tmem_ld32(tO + c * 32, wb);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) wb[e] = __float_as_uint(__uint_as_float(wb[e]) * alpha);
+                            tmem_st32(tO + c * 32, wb);
+                        }
+                        tmem_wait_st();
+                        l *= alpha;
+                        if (need) m = m_new;
+                        tmem_ld32(tS, wa);
+                    }
+                    m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+                    tmem_ld32(tS + 32, wb);
+                    ARC_TP(12);
                 }
-                ARC_TP(12);
-                ARC_TP(14);
-                // Pass 2: probabilities as bf16, each 32-key chunk over the first 16 of its own 32
-                // score columns; row sum in fp32.
-                const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t pk[16];
-                tmem_ld32(tS + 32, wb);
-                tmem_wait_ld();
-                chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc, rm);
-                tmem_st16(tS, pk);
-                tmem_ld32(tS + 64, wa);
-                chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
-                tmem_st16(tS + 32, pk);
-                tmem_ld32(tS + 96, wb);
-                tmem_wait_ld();
-                chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
-                tmem_st16(tS + 64, pk);
-                chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
-                tmem_st16(tS + 96, pk);
-                l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-                tmem_wait_st();
-                tc_fence_before_sync();
-                mbar_arrive(&p_full[s]);
-                ARC_TP(13);
+                // my turn?
+                {
+                    uint64_t* other = &turn[s ^ 1];
+                    const bool must = (s == 1) || gu > 0;
+                    const uint32_t parity = (uint32_t)((s == 1) ? gu : gu - 1) & 1u;
+                    if (must && !mbar_wait_warp(other, parity)) {
+                        report_fault(p.fault, FAULT_WAIT_FULL, 0x400u + s);
+                        ok = false;
+                        break;
+                    }
+                }
+                if (act) {
+                    ARC_TP(14);
+                    // Pass 2: probabilities as bf16, each 32-key chunk over the first 16 of its own 32
+                    // score columns; row sum in fp32.
+                    float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint32_t pk[16];
+                    tmem_wait_ld();
+                    if (full) {
+                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc, rm);
+                        tmem_st16(tS, pk);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
+                        tmem_st16(tS + 32, pk);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
+                        tmem_st16(tS + 64, pk);
+                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
+                        tmem_st16(tS + 96, pk);
+                    } else {
+                        chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc, rm);
+                        tmem_st16(tS, pk);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
+                        tmem_st16(tS + 32, pk);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
+                        tmem_st16(tS + 64, pk);
+                        chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
+                        tmem_st16(tS + 96, pk);
+                    }
+                    l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&p_full[s]);
+                    ++g;
+                    ARC_TP(13);
+                }
+                mbar_arrive(&turn[s]);
             }
             if (!ok) break;
+            if (hi == lo) {
+                // Nothing visible for this tile: zero output.
+                if (store) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
+                    for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                    if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
+                }
+                continue;
+            }
             ARC_TP(20);
 
             // Accumulator out: one thread writes the 256 contiguous bytes of its row.
