@@ -95,6 +95,15 @@ __device__ __forceinline__ PairWork decode_pair(const PrefillParams& p, const Ti
     return t;
 }
 
+// How 64 keys starting at kc relate to the 32 rows of a warp (warp-uniform answer).
+__device__ __forceinline__ int round_class(int kc, const RowMask& rm) {
+    const bool all = rm.lo <= kc && kc + 64 <= rm.hi;
+    const bool none = rm.hi <= kc || rm.lo >= kc + 64;
+    if (__all_sync(0xffffffffu, all)) return 0;
+    if (__all_sync(0xffffffffu, none)) return 2;
+    return 1;
+}
+
 __global__ void __maxnreg__(PairCfg::MAX_REGS)
     sdpa_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -129,6 +138,9 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
     if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
     __syncthreads();
     if (*abort_slot) return;
+#ifdef ARC_TRACE_CTAS
+    const long long ck0 = clock64();
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
@@ -351,8 +363,17 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
 #ifndef ARC_TR_THREAD
 #define ARC_TR_THREAD 0
 #endif
-        const bool tr = p.trace && blockIdx.x == 0 && threadIdx.x == ARC_TR_THREAD;
-#define ARC_TP(code) do { if (tr && tpos < 200) { p.trace[2 * tpos] = (code); p.trace[2 * tpos + 1] = clock64(); ++tpos; } } while (0)
+#ifndef ARC_TR_CTA
+#define ARC_TR_CTA 0
+#endif
+#ifndef ARC_TR_MIN
+#define ARC_TR_MIN 0
+#endif
+        const bool tr = p.trace && blockIdx.x == ARC_TR_CTA && threadIdx.x == ARC_TR_THREAD;
+#ifndef ARC_TR_SKIP
+#define ARC_TR_SKIP 0
+#endif
+#define ARC_TP(code) do { if (tr && tpos < 200 && (code) >= ARC_TR_MIN && tq >= ARC_TR_SKIP) { p.trace[2 * tpos] = (code); p.trace[2 * tpos + 1] = clock64(); ++tpos; } } while (0)
 #else
 #define ARC_TP(code) do { } while (0)
 #endif
@@ -409,31 +430,28 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     // Every key of the block visible to every row of the warp (seven blocks in nine
                     // with a 1024-key window): no per-element tests and no per-chunk votes.
                     full = __all_sync(0xffffffffu, rm.lo <= kc && kc + C::BN <= rm.hi);
-                    // Pass 1: row maximum of the block (the next chunk loads while one is reduced).
+                    // Pass 1: row maximum of the block, 64 keys per round.  The loops are kept rolled and
+                    // the masked form has a single body: the kernel has to stay small enough for the
+                    // instruction cache, and the masked blocks (window edge, diagonal) are the cold code.
                     float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
                     float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                    tmem_ld32(tS, wa);
-                    tmem_ld32(tS + 32, wb);
-                    tmem_wait_ld();
-                    if (full) {
-                        chunk_max<0>(wa, mr, sl, kc, rm);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_max<0>(wb, mr, sl, kc + 32, rm);
-                        tmem_ld32(tS + 96, wb);
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 64) {
+                        // 0: all 64 keys visible to all 32 rows, 2: none to any, 1: mixed
+                        const int cls = full ? 0 : round_class(kc + c, rm);
+                        if (cls == 2) continue;
+                        tmem_ld32(tS + c, wa);
+                        tmem_ld32(tS + c + 32, wb);
                         tmem_wait_ld();
-                        chunk_max<0>(wa, mr, sl, kc + 64, rm);
-                        tmem_ld32(tS, wa);  // first chunk again, for the exponentials
-                        chunk_max<0>(wb, mr, sl, kc + 96, rm);
-                    } else {
-                        chunk_max_any<false>(wa, mr, ms, sl, kc, rm);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_max_any<false>(wb, mr, ms, sl, kc + 32, rm);
-                        tmem_ld32(tS + 96, wb);
-                        tmem_wait_ld();
-                        chunk_max_any<false>(wa, mr, ms, sl, kc + 64, rm);
-                        tmem_ld32(tS, wa);
-                        chunk_max_any<false>(wb, mr, ms, sl, kc + 96, rm);
+                        if (cls == 0) {
+                            chunk_max<0>(wa, mr, sl, kc + c, rm);
+                            chunk_max<0>(wb, mr, sl, kc + c + 32, rm);
+                        } else {
+                            chunk_max<1>(wa, ms, sl, kc + c, rm);
+                            chunk_max<1>(wb, ms, sl, kc + c + 32, rm);
+                        }
                     }
+                    tmem_ld32(tS, wa);  // first chunks again, for the exponentials
                     const float bm = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
                                            fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
                     const float m_new = fmaxf(m, bm);
@@ -482,34 +500,33 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                 if (act) {
                     ARC_TP(14);
                     // Pass 2: probabilities as bf16, each 32-key chunk over the first 16 of its own 32
-                    // score columns; row sum in fp32.
+                    // score columns; row sum in fp32.  Rolled, 64 keys per round.
                     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                     uint32_t pk[16];
-                    tmem_wait_ld();
-                    if (full) {
-                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc, rm);
-                        tmem_st16(tS, pk);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
-                        tmem_st16(tS + 32, pk);
-                        tmem_ld32(tS + 96, wb);
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 64) {
+                        const int cls = full ? 0 : round_class(kc + c, rm);
+                        if (c > 0 && cls != 2) {
+                            tmem_ld32(tS + c, wa);
+                            tmem_ld32(tS + c + 32, wb);
+                        }
                         tmem_wait_ld();
-                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
-                        tmem_st16(tS + 64, pk);
-                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
-                        tmem_st16(tS + 96, pk);
-                    } else {
-                        chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc, rm);
-                        tmem_st16(tS, pk);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
-                        tmem_st16(tS + 32, pk);
-                        tmem_ld32(tS + 96, wb);
-                        tmem_wait_ld();
-                        chunk_exp_any<false>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
-                        tmem_st16(tS + 64, pk);
-                        chunk_exp_any<false>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
-                        tmem_st16(tS + 96, pk);
+                        if (cls == 0) {
+                            chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + c, rm);
+                            tmem_st16(tS + c, pk);
+                            chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + c + 32, rm);
+                            tmem_st16(tS + c + 32, pk);
+                        } else if (cls == 1) {
+                            chunk_exp<1>(wa, pk, ls4, sl, m_eff, kc + c, rm);
+                            tmem_st16(tS + c, pk);
+                            chunk_exp<1>(wb, pk, ls4, sl, m_eff, kc + c + 32, rm);
+                            tmem_st16(tS + c + 32, pk);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) pk[e] = 0u;
+                            tmem_st16(tS + c, pk);
+                            tmem_st16(tS + c + 32, pk);
+                        }
                     }
                     l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
                     tmem_wait_st();
@@ -596,6 +613,9 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
 
     tc_fence_before_sync();
     __syncthreads();
+#ifdef ARC_TRACE_CTAS
+    if (threadIdx.x == 0 && p.trace) p.trace[800 + blockIdx.x] = clock64() - ck0;
+#endif
     if (warp == C::PRODUCER_WARP) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
