@@ -90,7 +90,8 @@ static int device_state(DeviceState** out) {
                 }
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
-            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<false>, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<true>, PairCfg::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, true>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false>, PrefillCfg<256>::SMEM_BYTES));
@@ -217,9 +218,9 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.out_lse = nullptr;
 #endif
 
-    // Experimental alternative for head dim 128: two query tiles per CTA (prefill_pair_sm100.cuh).  It passes
-    // the same parity tests but measures slower than the single-tile kernel so far, so it runs only when
-    // ARC_SDPA_PREFILL_KERNEL=pair is set (for A/B measurements).
+    // Head dim 128 with enough work to fill the device: two query tiles per CTA (prefill_pair_sm100.cuh),
+    // the faster kernel whenever every SM gets a pair of tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair
+    // overrides the choice (for A/B measurements).
     if (HD == 128 && plan.splits == 1 && !(kp.mask_type == 1 && kp.mask != nullptr)) {
         static const int forced = [] {
             const char* e = std::getenv("ARC_SDPA_PREFILL_KERNEL");
@@ -227,13 +228,14 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             return std::strcmp(e, "pair") == 0 ? 2 : (std::strcmp(e, "single") == 0 ? 1 : 0);
         }();
         const long long pair_tiles = (long long)((p->seq + 255) / 256) * p->nq * p->batch;
-        const bool use_pair = forced == 2;
+        const bool use_pair = forced == 2 || (forced == 0 && pair_tiles >= ds->sm_count);
         if (use_pair) {
             if (pair_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
             kp.q_tiles = (p->seq + 255) / 256;
             kp.total_tiles = (int)pair_tiles;
             const unsigned ctas = (unsigned)(pair_tiles < ds->sm_count ? pair_tiles : ds->sm_count);
-            sdpa_prefill_pair_kernel<<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            if (kp.gate) sdpa_prefill_pair_kernel<true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            else sdpa_prefill_pair_kernel<false><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
             g_launches.fetch_add(1, std::memory_order_relaxed);
             ARC_CUDA(cudaGetLastError());
             return ARC_OK;

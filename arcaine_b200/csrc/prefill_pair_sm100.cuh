@@ -7,10 +7,11 @@
 // columns), one Q buffer in shared memory.  The two pipelines share the K and V rings, which
 // one producer thread fills by TMA, so every key block is fetched once for 256 rows.
 //
-// Ideally the pipelines run out of phase: while the softmax warps of A turn S_A(j) into P_A(j),
-// the tensor pipe works for B (O_B += P_B V, S_B = Q_B K^T), and the other way round.  (Nothing
-// enforces the phase yet; measured, the two tend to fall into step, which is why this kernel is
-// still slower than the single-tile one and is not the default.)  Per block
+// The pipelines run out of phase: while the softmax warps of A turn S_A(j) into P_A(j), the
+// tensor pipe works for B (O_B += P_B V, S_B = Q_B K^T), and the other way round.  Left alone
+// they fall into step (both wait for the tensor pipe, then both fight for the ex2 unit), so the
+// phase is enforced: the softmax warps take turns at the exponentials, block by block, through
+// a pair of mbarriers.  Per block
 // and pipeline the issuer does   wait P(j);  O += P(j) V(j);  S(j+1) = Q K(j+1)^T   — P is
 // written over S, so the next scores can only follow the P V that reads them, and both come
 // from one thread, in order.  The two issuers sit on different instruction schedulers.
@@ -95,15 +96,7 @@ __device__ __forceinline__ PairWork decode_pair(const PrefillParams& p, const Ti
     return t;
 }
 
-// How 64 keys starting at kc relate to the 32 rows of a warp (warp-uniform answer).
-__device__ __forceinline__ int round_class(int kc, const RowMask& rm) {
-    const bool all = rm.lo <= kc && kc + 64 <= rm.hi;
-    const bool none = rm.hi <= kc || rm.lo >= kc + 64;
-    if (__all_sync(0xffffffffu, all)) return 0;
-    if (__all_sync(0xffffffffu, none)) return 2;
-    return 1;
-}
-
+template <bool GATE>  // the gated epilogue is an instance of its own: 13 KB of code the common kernel does not carry
 __global__ void __maxnreg__(PairCfg::MAX_REGS)
     sdpa_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -435,23 +428,30 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     // instruction cache, and the masked blocks (window edge, diagonal) are the cold code.
                     float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
                     float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 64) {
-                        // 0: all 64 keys visible to all 32 rows, 2: none to any, 1: mixed
-                        const int cls = full ? 0 : round_class(kc + c, rm);
-                        if (cls == 2) continue;
-                        tmem_ld32(tS + c, wa);
-                        tmem_ld32(tS + c + 32, wb);
+                    if (full) {
+                        // the hot path: the next chunk loads while one is reduced
+                        tmem_ld32(tS, wa);
+                        tmem_ld32(tS + 32, wb);
                         tmem_wait_ld();
-                        if (cls == 0) {
-                            chunk_max<0>(wa, mr, sl, kc + c, rm);
-                            chunk_max<0>(wb, mr, sl, kc + c + 32, rm);
-                        } else {
-                            chunk_max<1>(wa, ms, sl, kc + c, rm);
-                            chunk_max<1>(wb, ms, sl, kc + c + 32, rm);
+                        chunk_max<0>(wa, mr, sl, kc, rm);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_max<0>(wb, mr, sl, kc + 32, rm);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_max<0>(wa, mr, sl, kc + 64, rm);
+                        tmem_ld32(tS, wa);  // first chunk again, for the exponentials
+                        chunk_max<0>(wb, mr, sl, kc + 96, rm);
+                    } else {
+                        // cold path (window edge, diagonal): one 32-key chunk at a time through one body
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 32) {
+                            if (chunk_class(kc + c, rm) == 2) continue;
+                            tmem_ld32(tS + c, wb);
+                            tmem_wait_ld();
+                            chunk_max<1>(wb, ms, sl, kc + c, rm);
                         }
+                        tmem_ld32(tS, wa);
                     }
-                    tmem_ld32(tS, wa);  // first chunks again, for the exponentials
                     const float bm = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
                                            fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
                     const float m_new = fmaxf(m, bm);
@@ -503,29 +503,32 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     // score columns; row sum in fp32.  Rolled, 64 keys per round.
                     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                     uint32_t pk[16];
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 64) {
-                        const int cls = full ? 0 : round_class(kc + c, rm);
-                        if (c > 0 && cls != 2) {
-                            tmem_ld32(tS + c, wa);
-                            tmem_ld32(tS + c + 32, wb);
-                        }
+                    if (full) {
                         tmem_wait_ld();
-                        if (cls == 0) {
-                            chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + c, rm);
-                            tmem_st16(tS + c, pk);
-                            chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + c + 32, rm);
-                            tmem_st16(tS + c + 32, pk);
-                        } else if (cls == 1) {
-                            chunk_exp<1>(wa, pk, ls4, sl, m_eff, kc + c, rm);
-                            tmem_st16(tS + c, pk);
-                            chunk_exp<1>(wb, pk, ls4, sl, m_eff, kc + c + 32, rm);
-                            tmem_st16(tS + c + 32, pk);
-                        } else {
+                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc, rm);
+                        tmem_st16(tS, pk);
+                        tmem_ld32(tS + 64, wa);
+                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
+                        tmem_st16(tS + 32, pk);
+                        tmem_ld32(tS + 96, wb);
+                        tmem_wait_ld();
+                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
+                        tmem_st16(tS + 64, pk);
+                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
+                        tmem_st16(tS + 96, pk);
+                    } else {
+                        tmem_wait_ld();
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 32) {
+                            if (chunk_class(kc + c, rm) == 2) {
 #pragma unroll
-                            for (int e = 0; e < 16; ++e) pk[e] = 0u;
+                                for (int e = 0; e < 16; ++e) pk[e] = 0u;
+                            } else {
+                                tmem_ld32(tS + c, wb);
+                                tmem_wait_ld();
+                                chunk_exp<1>(wb, pk, ls4, sl, m_eff, kc + c, rm);
+                            }
                             tmem_st16(tS + c, pk);
-                            tmem_st16(tS + c + 32, pk);
                         }
                     }
                     l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
@@ -536,6 +539,71 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     ARC_TP(13);
                 }
                 mbar_arrive(&turn[s]);
+                if (act && j + 1 == hi) {
+                    // The tile's last key block is on its way: read the accumulator out now, before the
+                    // turns for the blocks only the other tile still uses.
+                    ARC_TP(20);
+
+                    // Accumulator out: one thread writes the 256 contiguous bytes of its row.
+                    if (!mbar_wait_warp(&o_full[s], tq & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_O, tq);
+                        ok = false;
+                        break;
+                    }
+                    ++tq;
+                    tc_fence_after_sync();
+                    ARC_TP(21);
+                    const float inv = l > 0.f ? 1.0f / l : 0.f;
+                    const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
+                    uint16_t* dst = p.out + eoff;
+                    const uint16_t* gp = GATE ? p.gate + eoff : nullptr;
+                    const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
+        #pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        tmem_ld32(tO + c * 32, wa);
+                        tmem_wait_ld();
+                        if (c == HD / 32 - 1) {
+                            // O is in registers: the next tile may overwrite the accumulator.
+                            tc_fence_before_sync();
+                            mbar_arrive(&o_empty[s]);
+                        }
+                        if (store) {
+        #pragma unroll
+                            for (int e = 0; e < 32; e += 16) {
+                                uint32_t ov[8];
+        #pragma unroll
+                                for (int hh = 0; hh < 2; ++hh) {
+                                    float o[8];
+        #pragma unroll
+                                    for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(wa[e + hh * 8 + u]) * inv;
+                                    if (gp) {
+                                        const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e + hh * 8);
+                                        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        #pragma unroll
+                                        for (int u = 0; u < 8; ++u) {
+                                            const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
+                                            const float sig = 1.0f / (1.0f + __expf(-gf));
+                                            o[u] = bf16_round(o[u]) * sig;
+                                        }
+                                    }
+        #pragma unroll
+                                    for (int u = 0; u < 4; ++u) ov[hh * 4 + u] = pack_bf16x2(o[2 * u], o[2 * u + 1]);
+                                }
+                                uint16_t* q = dst + c * 32 + e;
+                                if (wide) {
+                                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(ov[0]),
+                                                 "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]), "r"(ov[6]), "r"(ov[7])
+                                                 : "memory");
+                                } else {
+                                    *reinterpret_cast<uint4*>(q) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                                    *reinterpret_cast<uint4*>(q + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
+                                }
+                            }
+                        }
+                    }
+                    if (store && p.out_lse) p.out_lse[row] = lse;
+                    ARC_TP(22);
+                }
             }
             if (!ok) break;
             if (hi == lo) {
@@ -547,67 +615,6 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                 }
                 continue;
             }
-            ARC_TP(20);
-
-            // Accumulator out: one thread writes the 256 contiguous bytes of its row.
-            if (!mbar_wait_warp(&o_full[s], tq & 1)) {
-                report_fault(p.fault, FAULT_WAIT_O, tq);
-                ok = false;
-                break;
-            }
-            ++tq;
-            tc_fence_after_sync();
-            ARC_TP(21);
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
-            uint16_t* dst = p.out + eoff;
-            const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
-            const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
-#pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
-                tmem_ld32(tO + c * 32, wa);
-                tmem_wait_ld();
-                if (c == HD / 32 - 1) {
-                    // O is in registers: the next tile may overwrite the accumulator.
-                    tc_fence_before_sync();
-                    mbar_arrive(&o_empty[s]);
-                }
-                if (store) {
-#pragma unroll
-                    for (int e = 0; e < 32; e += 16) {
-                        uint32_t ov[8];
-#pragma unroll
-                        for (int hh = 0; hh < 2; ++hh) {
-                            float o[8];
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(wa[e + hh * 8 + u]) * inv;
-                            if (gp) {
-                                const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e + hh * 8);
-                                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
-                                    const float sig = 1.0f / (1.0f + __expf(-gf));
-                                    o[u] = bf16_round(o[u]) * sig;
-                                }
-                            }
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) ov[hh * 4 + u] = pack_bf16x2(o[2 * u], o[2 * u + 1]);
-                        }
-                        uint16_t* q = dst + c * 32 + e;
-                        if (wide) {
-                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(ov[0]),
-                                         "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]), "r"(ov[6]), "r"(ov[7])
-                                         : "memory");
-                        } else {
-                            *reinterpret_cast<uint4*>(q) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                            *reinterpret_cast<uint4*>(q + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
-                        }
-                    }
-                }
-            }
-            if (store && p.out_lse) p.out_lse[row] = lse;
-            ARC_TP(22);
         }
     }
 

@@ -98,15 +98,21 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Wait for the phase with the given parity to complete.  Gives up after
 // ~`limit_cycles` SM clocks (default: about a second) and returns false; the
 // caller records a fault and unwinds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          long long limit_cycles = 2000000000LL) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is one out-of-line function: waits are all over the kernels and their code
+// would otherwise be repeated at every site (the kernels have to fit the instruction cache).
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, long long limit_cycles) {
     long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3FFu) == 0 && clock64() - t0 > limit_cycles) return false;
     }
     return true;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          long long limit_cycles = 2000000000LL) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, limit_cycles);
 }
 
 // Same, with a warp-uniform answer (every lane polls; all must succeed), so the
