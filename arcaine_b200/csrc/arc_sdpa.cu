@@ -218,9 +218,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.out_lse = nullptr;
 #endif
 
-    // Head dim 128 with enough work to fill the device: two query tiles per CTA (prefill_pair_sm100.cuh),
-    // the faster kernel whenever every SM gets a pair of tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair
-    // overrides the choice (for A/B measurements).
+    // Head dim 128: two query tiles per CTA (prefill_pair_sm100.cuh) when that is the faster way to cover
+    // the tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair overrides the choice (for A/B measurements).
     if (HD == 128 && plan.splits == 1 && !(kp.mask_type == 1 && kp.mask != nullptr)) {
         static const int forced = [] {
             const char* e = std::getenv("ARC_SDPA_PREFILL_KERNEL");
@@ -228,7 +227,14 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             return std::strcmp(e, "pair") == 0 ? 2 : (std::strcmp(e, "single") == 0 ? 1 : 0);
         }();
         const long long pair_tiles = (long long)((p->seq + 255) / 256) * p->nq * p->batch;
-        const bool use_pair = forced == 2 || (forced == 0 && pair_tiles >= ds->sm_count);
+        // Measured: a pair of tiles costs 1.87 single tiles.  Tiles come in waves of one per SM, so the
+        // kernel with the cheaper whole number of waves wins (512 pair tiles on 148 SMs are 4 waves,
+        // the same rows as 1024 single tiles are 7: the single-tile kernel is then faster).
+        const long long single_tiles = (long long)plan.q_tiles * p->nq * p->batch;
+        const long long sms = ds->sm_count;
+        const double cost_pair = 1.87 * (double)((pair_tiles + sms - 1) / sms);
+        const double cost_single = (double)((single_tiles + sms - 1) / sms);
+        const bool use_pair = forced == 2 || (forced == 0 && cost_pair <= cost_single);
         if (use_pair) {
             if (pair_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
             kp.q_tiles = (p->seq + 255) / 256;

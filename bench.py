@@ -181,7 +181,7 @@ class Workload:
         mb = self.working_set_bytes() / 1e6
         if self.inputs_exceed_l2:
             return f"this rank's working set ({mb:.0f} MB) is larger than L2 (126 MB): steps timed back to back, no flush"
-        return f"this rank's working set ({mb:.0f} MB) could stay in L2 (126 MB): a 256 MB buffer is written between timed steps"
+        return f"this rank's working set ({mb:.0f} MB) could stay in L2 (126 MB): between timed steps a 256 MB buffer is written and another 256 MB read"
 
     def units_total(self) -> float:      # algorithmic units per step, whole job (all ranks)
         raise NotImplementedError
@@ -553,9 +553,13 @@ class Runner:
         return float(t.item())
 
     def flush_l2(self):
+        """Write 256 MB, then read another 256 MB: whatever the previous step left in L2 is gone, and
+        the lines that are left are clean, so the timed step does not pay for the flush's write-backs."""
         if self.flush_buf is None:
             self.flush_buf = self.torch.empty(256 << 20, dtype=self.torch.uint8, device=self.device)
+            self.flush_src = self.torch.zeros(64 << 20, dtype=self.torch.int32, device=self.device)
         self.flush_buf.zero_()
+        self.flush_sink = self.flush_src.sum()
 
     def time_steps(self, fn, steps, warmup, flush=False):
         """Device time of exactly `steps` calls (ms, max over ranks), CUDA events on the launching stream."""
