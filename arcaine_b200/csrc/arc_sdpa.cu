@@ -649,14 +649,23 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     kp.pos0 = p->pos0;
     kp.theta = p->theta;
     kp.eps = p->eps;
-    // One CTA works on one token at a time; eight CTAs per SM keep enough loads in flight.
+    // A CTA works on `tpc` consecutive tokens per round: enough (token, head) rows for its eight warps
+    // (each takes 512 / hd rows per pass), within the shared-memory angle table of 1024 pairs.
     const long long tokens = (long long)p->batch * p->seq;
-    const long long cap = (long long)ds->sm_count * 8;
-    const unsigned ctas = (unsigned)(tokens < cap ? tokens : cap);
+    if (tokens > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
+    const int rows = (p->q ? p->nq : 0) + (p->k_src ? p->nkv : 0) + (p->v_dst ? p->nkv : 0);
+    const int rows_per_pass = 8 * (512 / p->hd);
+    int tpc = (8 * rows_per_pass + rows - 1) / rows;  // about eight passes per warp and round
+    const int max_tpc = 1024 / (p->hd / 2);
+    if (tpc > max_tpc) tpc = max_tpc;
+    if (tpc < 1) tpc = 1;
+    const long long rounds = (tokens + tpc - 1) / tpc;
+    const long long cap = (long long)ds->sm_count * 8;  // eight CTAs per SM keep enough loads in flight
+    const unsigned ctas = (unsigned)(rounds < cap ? rounds : cap);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (p->hd == 128) qkv_prepare_kernel<128><<<ctas, 256, 0, st>>>(kp);
-    else if (p->hd == 256) qkv_prepare_kernel<256><<<ctas, 256, 0, st>>>(kp);
-    else qkv_prepare_kernel<512><<<ctas, 256, 0, st>>>(kp);
+    if (p->hd == 128) qkv_prepare_kernel<128><<<ctas, 256, 0, st>>>(kp, tpc);
+    else if (p->hd == 256) qkv_prepare_kernel<256><<<ctas, 256, 0, st>>>(kp, tpc);
+    else qkv_prepare_kernel<512><<<ctas, 256, 0, st>>>(kp, tpc);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
     return ARC_OK;

@@ -13,8 +13,9 @@
 // works on those rounded values.  cos / sin come from a caller table (seq x n_active_pairs, as
 // the reference's RopeTable) or are computed per token: angle = (offset + token) / theta^(2p/hd).
 //
-// Mapping: one CTA per token at a time (grid-stride), cos / sin of the token staged once in
-// shared memory and shared by all its heads (the reference's "Fused" mode), one warp per
+// Mapping: one CTA per group of consecutive tokens at a time (grid-stride), cos / sin of those
+// tokens staged once in shared memory and shared by all their heads (the reference's "Fused"
+// mode), one warp per
 // (token, head) row segment: a lane holds eight consecutive elements of the row's first half and
 // the matching eight of the second half (16-byte loads), so a rotation pair never leaves the lane
 // and a warp covers 4 / 2 / 1 rows at once for head dim 128 / 256 / 512.
@@ -65,13 +66,17 @@ __device__ __forceinline__ float bf16_rne(float x) {
 
 // 256 threads = 8 warps.  A row of HD values is held by HD/16 lanes, each with eight consecutive
 // values of the row's first half and the matching eight of the second half (two 16-byte loads),
-// so a warp works on 32 / (HD/16) rows at once: 4 (HD 128), 2 (HD 256) or 1 (HD 512).
+// so a warp works on 32 / (HD/16) rows at once: 4 (HD 128), 2 (HD 256) or 1 (HD 512).  A CTA
+// takes `tpc` consecutive tokens per round (the host picks tpc so that a round has work for all
+// eight warps even when a rank holds only a few heads).
 template <int HD>
-__global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams p) {
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams p, const int tpc) {
     constexpr int LPR = HD / 16;    // lanes per row
     constexpr int RPW = 32 / LPR;   // rows per warp and pass
-    __shared__ float s_cos2[2][HD / 2];  // double-buffered: one barrier per token is enough
-    __shared__ float s_sin2[2][HD / 2];
+    constexpr int MAX_TPC = 1024 / (HD / 2);
+    __shared__ float s_cos2[2][1024];  // [round parity][token in round][pair]: one barrier per round is enough
+    __shared__ float s_sin2[2][1024];
+    __shared__ float s_inv[HD / 2];    // rotation frequencies, computed once
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPR;     // which of the warp's rows
@@ -80,20 +85,27 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
     const int rows_k = p.k_src && p.k_dst ? p.nkv : 0;
     const int rows_v = p.v_dst ? p.nkv : 0;
     const int rows = rows_q + rows_k + rows_v;
-    const long long tokens = (long long)p.batch * p.seq;
+    const int tokens = p.batch * p.seq;  // the host refuses more than 2^31 - 1 tokens
+    const int rounds = (tokens + tpc - 1) / tpc;
+    (void)MAX_TPC;
 
-    // HD / 2 <= 256 = blockDim.x: thread pr owns rotation pair pr, whose frequency never changes.
-    const float inv_freq = (threadIdx.x < p.nap && !p.rope_cos)
-                               ? 1.0f / powf(p.theta, 2.0f * threadIdx.x / static_cast<float>(HD)) : 0.f;
+    if (p.nap > 0 && !p.rope_cos) {
+        for (int pr = threadIdx.x; pr < p.nap; pr += blockDim.x)
+            s_inv[pr] = 1.0f / powf(p.theta, 2.0f * pr / static_cast<float>(HD));
+        __syncthreads();
+    }
     int it = 0;
-    for (long long tk = blockIdx.x; tk < tokens; tk += gridDim.x, ++it) {
-        const int b = static_cast<int>(tk / p.seq);
-        const int t = static_cast<int>(tk - (long long)b * p.seq);
+    for (int rd = blockIdx.x; rd < rounds; rd += gridDim.x, ++it) {
+        const int tk0 = rd * tpc;
         float* s_cos = s_cos2[it & 1];
         float* s_sin = s_sin2[it & 1];
         if (p.nap > 0) {
-            const int pr = threadIdx.x;
-            if (pr < p.nap) {
+            for (int idx = threadIdx.x; idx < tpc * p.nap; idx += blockDim.x) {
+                const int tl = idx / p.nap, pr = idx - tl * p.nap;
+                const int tk = tk0 + tl;
+                if (tk >= tokens) break;
+                const int b = tk / p.seq;
+                const int t = tk - b * p.seq;
                 float c, s;
                 if (p.rope_cos) {
                     const long long ti = (long long)b * p.rope_stride_b + (long long)t * p.nap + pr;
@@ -101,37 +113,45 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     s = p.rope_sin[ti];
                 } else {
                     const int pos = (p.pos_offset ? p.pos_offset[b] : p.pos0) + t;
-                    sincosf(static_cast<float>(pos) * inv_freq, &s, &c);
+                    sincosf(static_cast<float>(pos) * s_inv[pr], &s, &c);
                 }
-                s_cos[pr] = c;
-                s_sin[pr] = s;
+                s_cos[tl * (HD / 2) + pr] = c;
+                s_sin[tl * (HD / 2) + pr] = s;
             }
-            // Writers of this buffer two tokens ago were read before every thread reached the
-            // previous token's barrier, so one barrier per token orders both directions.
+            // Readers of this buffer two rounds ago finished before every thread reached the
+            // previous round's barrier, so one barrier per round orders both directions.
             __syncthreads();
         }
-        for (int r0 = warp * RPW; r0 < rows; r0 += 8 * RPW) {
-            const int r = r0 + sub;
-            const bool valid = r < rows;
+        const int slots = tpc * rows;  // (token in round, row) pairs of this round
+        for (int r0 = warp * RPW; r0 < slots; r0 += 8 * RPW) {
+            const int slot = r0 + sub;
+            const int tl = slot / rows;
+            const int r = slot - tl * rows;
+            const int tk = tk0 + tl;
+            const bool valid = slot < slots && tk < tokens;
+            const int b = valid ? tk / p.seq : 0;
+            const int t = valid ? tk - b * p.seq : 0;
             const uint16_t* src = nullptr;
             uint16_t* dst = nullptr;
             const uint16_t* weight = nullptr;
             bool rope = false;
-            if (r < rows_q) {
-                src = dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
-                weight = p.q_weight;
-                rope = true;
-            } else if (r < rows_q + rows_k) {
-                const int h = r - rows_q;
-                src = p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
-                dst = p.k_dst + b * p.kd_stride_b + t * p.kd_stride_t + (long long)h * HD;
-                weight = p.k_weight;
-                rope = true;
-            } else if (valid) {
-                const int h = r - rows_q - rows_k;
-                src = p.v_src ? p.v_src + b * p.vs_stride_b + t * p.vs_stride_t + (long long)h * HD
-                              : p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
-                dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
+            if (valid) {
+                if (r < rows_q) {
+                    src = dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
+                    weight = p.q_weight;
+                    rope = true;
+                } else if (r < rows_q + rows_k) {
+                    const int h = r - rows_q;
+                    src = p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
+                    dst = p.k_dst + b * p.kd_stride_b + t * p.kd_stride_t + (long long)h * HD;
+                    weight = p.k_weight;
+                    rope = true;
+                } else {
+                    const int h = r - rows_q - rows_k;
+                    src = p.v_src ? p.v_src + b * p.vs_stride_b + t * p.vs_stride_t + (long long)h * HD
+                                  : p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
+                    dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
+                }
             }
             float lo[8], hi[8];
             uint4 rl = make_uint4(0u, 0u, 0u, 0u), rh = rl;
@@ -164,11 +184,13 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                 }
             }
             if (rope) {
+                const float* tc = s_cos + tl * (HD / 2);
+                const float* ts = s_sin + tl * (HD / 2);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const int pr = li * 8 + e;
                     if (pr < p.nap) {
-                        const float c = s_cos[pr], s = s_sin[pr];
+                        const float c = tc[pr], s = ts[pr];
                         const float x0 = lo[e], x1 = hi[e];
                         lo[e] = x0 * c - x1 * s;
                         hi[e] = x0 * s + x1 * c;
