@@ -646,8 +646,8 @@ def cpu_sample(workload: str, reps: int = 1):
     if workload in ("prefill_window", "canvas"):
         if workload == "prefill_window":
             c = CFG3
-            S, L, nq, nkv, hd = c["S"], c["S"], 4, 2, c["hd"]
-            sample = "1 of 4 sequences, 4 of 32 query heads (2 KV heads), full 8192 tokens, window 1024"
+            S, L, nq, nkv, hd = c["S"], c["S"], c["nq"], c["nkv"], c["hd"]
+            sample = "1 of 4 sequences, all 32 query heads (16 KV heads), full 8192 tokens, window 1024"
             flops = cfg3_flops(1, nq)
             kw = dict(past_offset=0, sliding_window=c["W"], causal=True)
         else:
