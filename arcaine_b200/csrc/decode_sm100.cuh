@@ -453,18 +453,31 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
         if (z > 0.f) {
             inv = 1.f / z;
             lse = mx + __logf(z);
-            // each warp folds every 8th record; a lane owns VPL consecutive output values
-            for (int i = warp; i < n_parts; i += MERGE_THREADS / 32) {
-                const float w = wgt[i];
-                if (w == 0.f) continue;
-                const float* src = p.part_o + ((part0 + i) * p.nq + h) * HD + lane * VPL;
+            // each warp folds every 8th record, four at a time so that their loads are in flight
+            // together (one record after the other, the loop ran at one L2 latency per record);
+            // a lane owns VPL consecutive output values
+            constexpr int NW = MERGE_THREADS / 32, U = 4;
+            for (int i0 = warp; i0 < n_parts; i0 += NW * U) {
+                float w[U];
+                float4 ov[U][VPL / 4];
 #pragma unroll
-                for (int j = 0; j < VPL; j += 4) {
-                    const float4 ov = *reinterpret_cast<const float4*>(src + j);
-                    acc[j] = fmaf(w, ov.x, acc[j]);
-                    acc[j + 1] = fmaf(w, ov.y, acc[j + 1]);
-                    acc[j + 2] = fmaf(w, ov.z, acc[j + 2]);
-                    acc[j + 3] = fmaf(w, ov.w, acc[j + 3]);
+                for (int u = 0; u < U; ++u) {
+                    const int i = i0 + u * NW;
+                    w[u] = i < n_parts ? wgt[i] : 0.f;
+                    const float* src = p.part_o + ((part0 + i) * p.nq + h) * HD + lane * VPL;
+#pragma unroll
+                    for (int j = 0; j < VPL / 4; ++j)
+                        ov[u][j] = w[u] != 0.f ? *reinterpret_cast<const float4*>(src + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+#pragma unroll
+                    for (int j = 0; j < VPL / 4; ++j) {
+                        acc[4 * j] = fmaf(w[u], ov[u][j].x, acc[4 * j]);
+                        acc[4 * j + 1] = fmaf(w[u], ov[u][j].y, acc[4 * j + 1]);
+                        acc[4 * j + 2] = fmaf(w[u], ov[u][j].z, acc[4 * j + 2]);
+                        acc[4 * j + 3] = fmaf(w[u], ov[u][j].w, acc[4 * j + 3]);
+                    }
                 }
             }
         }
