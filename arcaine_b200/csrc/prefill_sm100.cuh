@@ -1,4 +1,6 @@
-// GQA flash-attention prefill / canvas kernel for sm_100a.
+// GQA flash-attention prefill / canvas kernel for sm_100a, one query tile at a time per CTA: the
+// kernel for head dim 256, additive masks, key-range splits and small problems (head dim 128
+// with enough tiles runs two tiles per CTA, prefill_pair_sm100.cuh).
 //
 // One CTA owns a tile of 128 query tokens of one query head and walks the key
 // blocks (128 keys) that tile can see.  Q, K and V tiles are staged in shared
@@ -6,7 +8,7 @@
 // S = Q K^T and O += P V run on the tcgen05 tensor cores with both accumulators
 // in tensor memory; P is written back to tensor memory as bf16 over the S
 // columns and fed to the second MMA from there, so probabilities never touch
-// shared or global memory.  Softmax is online, fp32, one query row per thread.
+// shared or global memory.  Softmax is online, fp32.
 //
 // Warp roles: eight softmax / correction / epilogue warps, two threads per query row
 // (warp index mod 4 selects the 32 TMEM lanes, warp index / 4 the 64-key half of each

@@ -213,3 +213,23 @@ def test_block_id_mask_matches_a_numpy_restatement():
         assert np.array_equal(oracle.fill_causal_mask_with_block_ids(None, q_len, kv_len, past, window),
                               oracle.fill_causal_mask(q_len, kv_len, past, window))
     assert np.isfinite(oracle.fill_causal_mask_with_block_ids(ids, q_len, kv_len, past)[4, 23])  # q=34 sees k=37
+
+
+PRE_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "preprocess_small.npz")
+
+
+def test_preprocess_fixtures():
+    """Committed fixtures for the pre-processing restatements (made by tests/golden/make_golden.py from torch /
+    numpy formulations): RMSNorm + RoPE within one bf16 step, the vision-block mask exactly."""
+    z = np.load(PRE_GOLDEN)
+    for name in ("hd128_full", "hd256_quarter", "hd512_norm_only"):
+        tokens, heads, hd, nap, offset = (int(v) for v in z[name + "_params"])
+        x = oracle.bits_to_bf16(z[name + "_x"]).reshape(tokens, heads, hd)
+        w = oracle.bits_to_bf16(z[name + "_w"])
+        want = oracle.bits_to_bf16(z[name + "_y"]).reshape(tokens, heads, hd).float()
+        got = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, offset=offset, theta=10000.0).float()
+        assert ((got - want).abs() <= want.abs() * 2.0 ** -7 + 1e-30).all(), name
+        assert (got != want).float().mean() < 5e-3, name
+    q_len, kv_len, past, window = (int(v) for v in z["blockmask_params"])
+    m = oracle.fill_causal_mask_with_block_ids(z["blockmask_ids"], q_len, kv_len, past, window)
+    assert np.array_equal(np.isneginf(m), z["blockmask_hidden"])

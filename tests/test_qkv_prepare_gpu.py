@@ -110,3 +110,18 @@ def test_rejects_bad_arguments(ops):
     with pytest.raises(ValueError, match="capacity"):
         ops.qkv_prepare(None, k, k, k_cache=torch.zeros(3, 2, 128, dtype=torch.bfloat16, device="cuda"),
                         v_cache=torch.zeros(3, 2, 128, dtype=torch.bfloat16, device="cuda"), past_len=0)
+
+
+def test_against_committed_fixtures(ops):
+    """The kernel against tests/golden/preprocess_small.npz (torch-fp32 formulation, see make_golden.py)."""
+    import os
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "preprocess_small.npz"))
+    for name in ("hd128_full", "hd256_quarter", "hd512_norm_only"):
+        tokens, heads, hd, nap, offset = (int(v) for v in z[name + "_params"])
+        x = oracle.bits_to_bf16(z[name + "_x"]).reshape(tokens, heads, hd)
+        w = oracle.bits_to_bf16(z[name + "_w"])
+        want = oracle.bits_to_bf16(z[name + "_y"]).reshape(tokens, heads, hd)
+        xd = x.cuda()
+        ops.fused_norm_rope_inplace(xd, w.cuda(), offset, 10000.0, 2.0 * nap / hd, 1e-6)
+        close_bf16(xd, want, name)
