@@ -183,7 +183,7 @@ def test_norm_rope_restatement_matches_torch(hd, partial):
         got = oracle.norm_rope(x, weight, eps=1e-6, n_active_pairs=nap, offset=11, theta=10000.0)
         want = _torch_norm_rope(x, weight, 1e-6, nap, 11, 10000.0)
         diff = (got.float() - want.float()).abs()
-        step = want.float().abs() * 2.0 ** -7 + 1e-30
+        step = want.float().abs() * 2.0 ** -7 + 2e-6
         assert (diff <= step).all()
         assert (got != want).float().mean() < 5e-3
     # table mode reads the angles instead of computing them
@@ -228,7 +228,7 @@ def test_preprocess_fixtures():
         w = oracle.bits_to_bf16(z[name + "_w"])
         want = oracle.bits_to_bf16(z[name + "_y"]).reshape(tokens, heads, hd).float()
         got = oracle.norm_rope(x, w, eps=1e-6, n_active_pairs=nap, offset=offset, theta=10000.0).float()
-        assert ((got - want).abs() <= want.abs() * 2.0 ** -7 + 1e-30).all(), name
+        assert ((got - want).abs() <= want.abs() * 2.0 ** -7 + 2e-6).all(), name
         assert (got != want).float().mean() < 5e-3, name
     q_len, kv_len, past, window = (int(v) for v in z["blockmask_params"])
     m = oracle.fill_causal_mask_with_block_ids(z["blockmask_ids"], q_len, kv_len, past, window)

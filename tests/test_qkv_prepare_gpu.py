@@ -15,10 +15,11 @@ def ops():
 
 
 def close_bf16(got, want, what):
-    """At most one bf16 step apart, and only in a small share of the elements (the device sums the squares
-    in fp32 with rsqrt.approx, the oracle in double)."""
+    """At most one bf16 step apart (plus 2e-6 absolute: a rotation can cancel to nearly zero, where fp32
+    rounding of the O(1) operands is all that is left), and only in a small share of the elements (the
+    device sums the squares in fp32 with rsqrt.approx, the oracle in double)."""
     g, w = got.detach().cpu().float(), want.float()
-    step = w.abs() * 2.0 ** -7 + 1e-30
+    step = w.abs() * 2.0 ** -7 + 2e-6
     assert ((g - w).abs() <= step).all(), f"{what}: max diff {(g - w).abs().max().item()}"
     assert (g != w).float().mean().item() < 5e-3, f"{what}: too many one-step differences"
 
