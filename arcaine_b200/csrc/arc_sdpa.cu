@@ -92,10 +92,12 @@ static int device_state(DeviceState** out) {
             }
             ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<false>, PairCfg::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<true>, PairCfg::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false>, PrefillCfg<128>::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, true>, PrefillCfg<128>::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false>, PrefillCfg<256>::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, true>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, false>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, true>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, true, true>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, false>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, true>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, true, true>, PrefillCfg<256>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 1>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
@@ -256,9 +258,11 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     const unsigned ctas = (unsigned)(total_tiles < ds->sm_count ? total_tiles : ds->sm_count);
     // The additive-mask form is a kernel of its own: the common one stays small.
     if (kp.mask_type == 1 && kp.mask != nullptr)
-        sdpa_prefill_kernel<HD, true><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+        sdpa_prefill_kernel<HD, true, true><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+    else if (kp.gate && plan.splits == 1)
+        sdpa_prefill_kernel<HD, false, true><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
     else
-        sdpa_prefill_kernel<HD, false><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+        sdpa_prefill_kernel<HD, false, false><<<ctas, PrefillCfg<HD>::THREADS, PrefillCfg<HD>::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
 

@@ -323,7 +323,9 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
     return t;
 }
 
-template <int HD, bool ADD_MASK>
+// ADD_MASK and GATE select code that most calls do not need (an additive mask row per query, the
+// sigmoid-gated epilogue); the common instance carries neither and stays small.
+template <int HD, bool ADD_MASK, bool GATE>
 __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -751,7 +753,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             } else {
                 const long long eoff = tw.b * p.o_stride_b + t * p.o_stride_t + (long long)tw.h * HD + kh * OC;
                 uint16_t* dst = p.out + eoff;
-                const uint16_t* gp = p.gate ? p.gate + eoff : nullptr;
+                const uint16_t* gp = (GATE && p.gate) ? p.gate + eoff : nullptr;
                 // One thread writes 128 (or 256) contiguous bytes of its row.  When the row is 32-byte
                 // aligned this goes out as 256-bit stores, each a whole DRAM sector.
                 const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
