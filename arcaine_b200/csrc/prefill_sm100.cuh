@@ -199,6 +199,25 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk
             unpack_f32x2(acc[u], a, b);
             ls[u] += a + b;
         }
+    } else if constexpr (MODE == 1) {
+        // Per-row span: the same packed arithmetic, plus one select per score (exp2(-inf) = 0).
+        const uint64_t sl2 = pack_f32x2(sl, sl);
+        const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
+        const int lo_rel = rm.lo - key0, hi_rel = rm.hi - key0;  // visible: lo_rel <= e < hi_rel
+        uint64_t acc[2] = {0ull, 0ull};
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), sl2, nm2), x0, x1);
+            const float p0 = fast_exp2((e >= lo_rel && e < hi_rel) ? x0 : -CUDART_INF_F);
+            const float p1 = fast_exp2((e + 1 >= lo_rel && e + 1 < hi_rel) ? x1 : -CUDART_INF_F);
+            acc[(e >> 1) & 1] = add_f32x2(acc[(e >> 1) & 1], pack_f32x2(p0, p1));
+            pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+        float a, b, c, d;
+        unpack_f32x2(acc[0], a, b);
+        unpack_f32x2(acc[1], c, d);
+        ls[0] += (a + b) + (c + d);
     } else {
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
