@@ -559,15 +559,7 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     uint16_t* dst = p.out + eoff;
                     const uint16_t* gp = GATE ? p.gate + eoff : nullptr;
                     const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
-        #pragma unroll 1
-                    for (int c = 0; c < HD / 32; ++c) {
-                        tmem_ld32(tO + c * 32, wa);
-                        tmem_wait_ld();
-                        if (c == HD / 32 - 1) {
-                            // O is in registers: the next tile may overwrite the accumulator.
-                            tc_fence_before_sync();
-                            mbar_arrive(&o_empty[s]);
-                        }
+                    auto store_chunk = [&](const uint32_t (&w)[32], int c) {
                         if (store) {
         #pragma unroll
                             for (int e = 0; e < 32; e += 16) {
@@ -576,7 +568,7 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                                 for (int hh = 0; hh < 2; ++hh) {
                                     float o[8];
         #pragma unroll
-                                    for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(wa[e + hh * 8 + u]) * inv;
+                                    for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(w[e + hh * 8 + u]) * inv;
                                     if (gp) {
                                         const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e + hh * 8);
                                         const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
@@ -601,6 +593,20 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                                 }
                             }
                         }
+                    };
+                    // two 32-column chunks per round: their loads are in flight together
+        #pragma unroll 1
+                    for (int c = 0; c < HD / 32; c += 2) {
+                        tmem_ld32(tO + c * 32, wa);
+                        tmem_ld32(tO + c * 32 + 32, wb);
+                        tmem_wait_ld();
+                        if (c + 2 == HD / 32) {
+                            // O is in registers: the next tile may overwrite the accumulator.
+                            tc_fence_before_sync();
+                            mbar_arrive(&o_empty[s]);
+                        }
+                        store_chunk(wa, c);
+                        store_chunk(wb, c + 1);
                     }
                     if (store && p.out_lse) p.out_lse[row] = lse;
                     ARC_TP(22);
