@@ -241,18 +241,16 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
             const uint64_t dQ = make_smem_desc_sw128(smem_u32(sQ + s * C::TILE_BYTES), 16, 1024);
             const uint64_t dK = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
             const uint64_t dV = make_smem_desc_sw128(smem_u32(sV), C::CHUNK_BYTES, 1024);
-            uint64_t aQ[8], bK0[8], bK1[8], bV0[8], bV1[8];
+            uint64_t aQ[8], bK[8], bV[8];  // K and V: stage 0; the other stage is TILE_BYTES further
             uint32_t aP[8];
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
                 const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim columns
                 aQ[kk] = dQ + o;
-                bK0[kk] = dK + o;
-                bK1[kk] = dK + o + (C::TILE_BYTES >> 4);
+                bK[kk] = dK + o;
                 // 16 keys of V: 8-key groups 1024 bytes apart; of P: 8 packed columns, each 32-key
                 // chunk at the start of its own 32 score columns
-                bV0[kk] = dV + ((kk * 2048) >> 4);
-                bV1[kk] = dV + ((kk * 2048) >> 4) + (C::TILE_BYTES >> 4);
+                bV[kk] = dV + ((kk * 2048) >> 4);
                 aP[kk] = tS + (kk >> 1) * 32 + (kk & 1) * 8;
             }
             static_assert(KS == 2 && VS == 2 && HD == 128, "descriptor tables assume two stages and head dim 128");
@@ -272,8 +270,13 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     return true;
                 }
                 tc_fence_after_sync();
-                if (r & 1) umma_ss_x8(tS, aQ, bK1, IDESC_QK, 0u);
-                else umma_ss_x8(tS, aQ, bK0, IDESC_QK, 0u);
+                {
+                    uint64_t b[8];
+                    const uint64_t stage = (uint64_t)((r & 1) * (C::TILE_BYTES >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) b[kk] = bK[kk] + stage;
+                    umma_ss_x8(tS, aQ, b, IDESC_QK, 0u);
+                }
                 umma_commit(&s_full[s]);
                 umma_commit(&k_empty[r % KS]);
                 if (last) umma_commit(&q_empty[s]);
@@ -288,19 +291,18 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     report_fault(p.fault, FAULT_WAIT_Q, tq);
                     break;
                 }
-                for (int j = pw.ulo; ok && j < pw.uhi; ++j, ++gu) {
+                // Position j: O += P(j) V(j), then S(j+1).  The loop starts one position early, so that
+                // the tile's first scores come out of the same (single) place in the code.
+                for (int j = pw.ulo - 1; ok && j < pw.uhi; ++j) {
                     const bool act = j >= lo && j < hi;
-                    if (j == pw.ulo) {
-                        ok = scores(gu, act, act && j + 1 == hi);
-                        if (!ok) break;
-                    }
-                    // O += P(j) V(j)
-                    if (!mbar_wait(&v_full[gu % VS], (gu / VS) & 1)) {
+                    if (j >= pw.ulo && !mbar_wait(&v_full[gu % VS], (gu / VS) & 1)) {
                         report_fault(p.fault, FAULT_WAIT_V, gu);
                         ok = false;
                         break;
                     }
-                    if (act) {
+                    if (j < pw.ulo) {
+                        // nothing to accumulate yet
+                    } else if (act) {
                         if (!mbar_wait(&p_full[s], g & 1)) {
                             report_fault(p.fault, FAULT_WAIT_P, g);
                             ok = false;
@@ -315,8 +317,13 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                         // P from tensor memory: each 32-key chunk keeps its 16 bf16x2 columns at the
                         // start of its own 32 score columns.  V is MN-major: 64-element head-dim
                         // chunks 16 KB apart, 8-key groups 1024 bytes apart.
-                        if (gu & 1) umma_ts_x8(tO, aP, bV1, IDESC_PV, j > lo ? 1u : 0u);
-                        else umma_ts_x8(tO, aP, bV0, IDESC_PV, j > lo ? 1u : 0u);
+                        {
+                            uint64_t b[8];
+                            const uint64_t stage = (uint64_t)((gu & 1) * (C::TILE_BYTES >> 4));
+#pragma unroll
+                            for (int kk = 0; kk < 8; ++kk) b[kk] = bV[kk] + stage;
+                            umma_ts_x8(tO, aP, b, IDESC_PV, j > lo ? 1u : 0u);
+                        }
                         umma_commit(&v_empty[gu % VS]);
                         umma_commit(&pv_done[s]);
                         if (j + 1 == hi) umma_commit(&o_full[s]);
@@ -324,10 +331,11 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
                     } else {
                         mbar_arrive(&v_empty[gu % VS]);
                     }
+                    if (j >= pw.ulo) ++gu;  // ring position of block j + 1 from here on
                     // S(j+1): over the P just consumed, behind the MMAs that read it
                     if (j + 1 < pw.uhi) {
                         const bool act1 = j + 1 >= lo && j + 1 < hi;
-                        ok = scores(gu + 1, act1, act1 && j + 2 == hi);
+                        ok = scores(gu, act1, act1 && j + 2 == hi);
                     }
                 }
                 if (hi > lo) ++tq;
