@@ -249,11 +249,32 @@ class PrefillWindow(Workload):
                               window=CFG3["W"], out=self.out)
 
     def step_e2e(self):
-        self.q.copy_(self.hq, non_blocking=True)
-        self.k.copy_(self.hk, non_blocking=True)
-        self.v.copy_(self.hv, non_blocking=True)
-        self.step()
-        self.hout.copy_(self.out, non_blocking=True)
+        """Host buffers in, host buffers out, through ops.sdpa_prefill: one call per sequence, so that the
+        copy-in of sequence b+1, the kernel of b and the copy-out of b-1 overlap (two copy streams)."""
+        torch = self.torch
+        cur = torch.cuda.current_stream()
+        if not hasattr(self, "s_in"):
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            self.ev_in = [torch.cuda.Event() for _ in range(self.B)]
+            self.ev_done = [torch.cuda.Event() for _ in range(self.B)]
+            for e in self.ev_done:
+                e.record(cur)
+        for b in range(self.B):
+            self.s_in.wait_event(self.ev_done[b])  # the previous step's kernel no longer reads these inputs
+            with torch.cuda.stream(self.s_in):
+                self.q[b].copy_(self.hq[b], non_blocking=True)
+                self.k[b].copy_(self.hk[b], non_blocking=True)
+                self.v[b].copy_(self.hv[b], non_blocking=True)
+                self.ev_in[b].record(self.s_in)
+        for b in range(self.B):
+            cur.wait_event(self.ev_in[b])
+            self.ops.sdpa_prefill(self.q[b:b + 1], self.k[b:b + 1], self.v[b:b + 1], scale=self.scale,
+                                  mask_type=self.ops.MASK_CAUSAL, window=CFG3["W"], out=self.out[b:b + 1])
+            self.ev_done[b].record(cur)
+            self.s_out.wait_event(self.ev_done[b])
+            with torch.cuda.stream(self.s_out):
+                self.hout[b].copy_(self.out[b], non_blocking=True)
+        cur.wait_stream(self.s_out)  # the step ends when its result is on the host
 
     def config(self):
         c = CFG3
