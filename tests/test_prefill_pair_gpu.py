@@ -41,6 +41,21 @@ for i, (seq, kv, nq, nkv, mt, w, gate) in enumerate(cases):
     finite = torch.isfinite(want[2])
     assert torch.equal(torch.isfinite(lse.cpu()), finite), f"case {i}: lse finiteness"
     assert torch.allclose(lse.cpu()[finite], want[2][finite], atol=2e-3), f"case {i}: lse"
+# Scores that grow along the keys: the one-pass blocks must move their reference, both between blocks
+# (growth of 2^8 .. 2^32) and inside a block (more than 2^32), without losing accuracy.
+for i, (seq, kv, gain_at, gain) in enumerate([(384, 1024, 512, 6.0), (384, 1024, 300, 60.0), (256, 2048, 1900, 200.0),
+                                              (300, 1500, 130, 25.0)]):
+    q, k, v = seeded_bf16(seq, 4, 128, seed=1200 + i), seeded_bf16(kv, 2, 128, seed=1250 + i), seeded_bf16(kv, 2, 128, seed=1290 + i)
+    k = k.float()
+    k[gain_at:] *= gain
+    k[gain_at + 37::53] *= 3.0   # and a few outliers inside the blocks
+    k = k.bfloat16()
+    for mt in (0, 3):
+        out, lse = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=0.09, mask_type=mt, num_splits=1, return_lse=True)
+        want = oracle.sdpa_f32(q, k, v, scale=0.09, mask_type=mt, want_lse=True)
+        assert_close(out, want[0], f"growing scores {i} mask {mt}")
+        finite = torch.isfinite(want[2])
+        assert torch.allclose(lse.cpu()[finite], want[2][finite], atol=2e-3, rtol=1e-5), f"growing scores {i}: lse"
 # batch > 1 and many tiles per CTA: against the default kernel's own parity-tested output is not possible in
 # this process, so check sampled rows against the oracle
 B, S, nq, nkv = 2, 4096, 16, 8
