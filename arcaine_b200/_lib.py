@@ -81,6 +81,8 @@ class QkvPrepareParams(C.Structure):
         ("v_dst_stride_b", C.c_int64), ("v_dst_stride_t", C.c_int64),
         ("rope_stride_b", C.c_int64),
         ("pos0", C.c_int32), ("theta", C.c_float), ("eps", C.c_float),
+        ("rot_half", C.c_int32), ("freq_denom", C.c_int32), ("mrope_positions", C.c_void_p),
+        ("mrope_section", C.c_int32 * 3), ("v_copy", C.c_int32),
     ]
 
 

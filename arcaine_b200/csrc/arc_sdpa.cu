@@ -653,6 +653,16 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     kp.pos0 = p->pos0;
     kp.theta = p->theta;
     kp.eps = p->eps;
+    kp.rot_half = p->rot_half > 0 ? p->rot_half : p->hd / 2;
+    kp.freq_denom = p->freq_denom > 0 ? p->freq_denom : p->hd;
+    kp.mrope_pos = p->mrope_positions;
+    kp.sec1 = p->mrope_section[1];
+    kp.sec2 = p->mrope_section[2];
+    kp.v_copy = p->v_copy ? 1 : 0;
+    if (kp.rot_half != p->hd / 2) {
+        const int rh = kp.rot_half;
+        if (rh < 8 || (rh & (rh - 1)) != 0 || rh > p->hd / 4 || p->n_active_pairs > rh) return ARC_ERR_BAD_SHAPE;
+    }
     // A CTA works on `tpc` consecutive tokens per round: enough (token, head) rows for its eight warps
     // (each takes 512 / hd rows per pass), within the shared-memory angle table of 1024 pairs.
     const long long tokens = (long long)p->batch * p->seq;
@@ -667,9 +677,16 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     const long long cap = (long long)ds->sm_count * 8;  // eight CTAs per SM keep enough loads in flight
     const unsigned ctas = (unsigned)(rounds < cap ? rounds : cap);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (p->hd == 128) qkv_prepare_kernel<128><<<ctas, 256, 0, st>>>(kp, tpc);
-    else if (p->hd == 256) qkv_prepare_kernel<256><<<ctas, 256, 0, st>>>(kp, tpc);
-    else qkv_prepare_kernel<512><<<ctas, 256, 0, st>>>(kp, tpc);
+    const bool qwen = kp.rot_half != p->hd / 2 || kp.freq_denom != p->hd || kp.mrope_pos != nullptr || kp.v_copy;
+    if (qwen) {
+        if (p->hd == 128) qkv_prepare_kernel<128, true><<<ctas, 256, 0, st>>>(kp, tpc);
+        else if (p->hd == 256) qkv_prepare_kernel<256, true><<<ctas, 256, 0, st>>>(kp, tpc);
+        else qkv_prepare_kernel<512, true><<<ctas, 256, 0, st>>>(kp, tpc);
+    } else {
+        if (p->hd == 128) qkv_prepare_kernel<128, false><<<ctas, 256, 0, st>>>(kp, tpc);
+        else if (p->hd == 256) qkv_prepare_kernel<256, false><<<ctas, 256, 0, st>>>(kp, tpc);
+        else qkv_prepare_kernel<512, false><<<ctas, 256, 0, st>>>(kp, tpc);
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
     return ARC_OK;

@@ -226,4 +226,36 @@ void qkv_norm_rope_append(cudaStream_t stream, bf16* Q, const bf16* K, const bf1
     throw_on(arc_qkv_prepare(&p, stream), "qkv_norm_rope_append");
 }
 
+void qwen35_norm_mrope_append(cudaStream_t stream, bf16* query, const bf16* key, const bf16* value, bf16* key_cache,
+                              bf16* value_cache, const int32_t* positions, int seq, int past, int query_heads,
+                              int key_heads, int head_dim, int rotary_dim, float theta, const int sections[3],
+                              const bf16* q_norm, const bf16* k_norm, float eps) {
+    if (!sections) throw std::runtime_error("Qwen3.5 MRoPE needs three sections");
+    arc_qkv_prepare_params p{};
+    const int64_t row = (int64_t)key_heads * head_dim;
+    p.q = query;
+    p.k_src = key;
+    p.v_src = value;
+    p.k_dst = key_cache + (int64_t)past * row;
+    p.v_dst = value_cache + (int64_t)past * row;
+    p.q_weight = q_norm;
+    p.k_weight = k_norm;
+    p.batch = 1;
+    p.seq = seq;
+    p.nq = query_heads;
+    p.nkv = key_heads;
+    p.hd = head_dim;
+    p.q_stride_t = (int64_t)query_heads * head_dim;
+    p.k_src_stride_t = p.v_src_stride_t = p.k_dst_stride_t = p.v_dst_stride_t = row;
+    p.n_active_pairs = rotary_dim / 2;
+    p.rot_half = rotary_dim / 2;
+    p.freq_denom = rotary_dim;
+    p.mrope_positions = positions;
+    for (int i = 0; i < 3; ++i) p.mrope_section[i] = sections[i];
+    p.v_copy = 1;
+    p.theta = theta;
+    p.eps = eps;
+    throw_on(arc_qkv_prepare(&p, stream), "qwen35_norm_mrope_append");
+}
+
 }  // namespace arcaine

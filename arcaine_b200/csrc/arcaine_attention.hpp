@@ -107,4 +107,12 @@ void qkv_norm_rope_append(cudaStream_t stream, bf16* Q, const bf16* K, const bf1
                           int seq, int past_len, int nq, int nkv, int hd, const bf16* q_norm, const bf16* k_norm,
                           float theta, float partial, float eps, const float* rope_cos, const float* rope_sin);
 
+// Qwen3.5 layer call (src/modeling/qwen3_5/operators.hpp:127-140) in one launch: rms_norm of Q and K with
+// their weights, qwen35_apply_mrope (src/modeling/qwen3_5/kernels.hpp:585-617) and the two cache memcpys.
+// positions: device int32 (3, seq); sections: the three mrope_section values.
+void qwen35_norm_mrope_append(cudaStream_t stream, bf16* query, const bf16* key, const bf16* value, bf16* key_cache,
+                              bf16* value_cache, const int32_t* positions, int seq, int past, int query_heads,
+                              int key_heads, int head_dim, int rotary_dim, float theta, const int sections[3],
+                              const bf16* q_norm, const bf16* k_norm, float eps);
+
 }  // namespace arcaine

@@ -45,7 +45,20 @@ struct QkvPrepareParams {
     long long rope_stride_b;  // elements between the tables of two sequences (0: shared)
     int pos0;
     float theta, eps;
+    // Qwen3.5 multi-axis RoPE (src/modeling/qwen3_5/kernels.hpp:576-617): pairs (f, f + rot_half) inside the
+    // first 2 * rot_half values of a row, frequency exponent 2 f / freq_denom, position taken from one of
+    // three axes per frequency.  rot_half == hd / 2 with no positions is the plain form.
+    int rot_half, freq_denom;
+    const int* mrope_pos;  // (batch, 3, seq) or nullptr
+    int sec1, sec2;        // sections of axes 1 and 2
+    int v_copy;            // V rows are copied, not normalised
 };
+
+__device__ __forceinline__ int mrope_axis(int f, int sec1, int sec2) {
+    if (f >= 1 && f < sec1 * 3 && f % 3 == 1) return 1;
+    if (f >= 2 && f < sec2 * 3 && f % 3 == 2) return 2;
+    return 0;
+}
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -69,7 +82,9 @@ __device__ __forceinline__ float bf16_rne(float x) {
 // so a warp works on 32 / (HD/16) rows at once: 4 (HD 128), 2 (HD 256) or 1 (HD 512).  A CTA
 // takes `tpc` consecutive tokens per round (the host picks tpc so that a round has work for all
 // eight warps even when a rank holds only a few heads).
-template <int HD>
+// QWEN: the Qwen3.5 form (pairs rot_half apart, per-axis positions, V copied); the common instance does not
+// carry its branches.
+template <int HD, bool QWEN>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams p, const int tpc) {
     constexpr int LPR = HD / 16;    // lanes per row
     constexpr int RPW = 32 / LPR;   // rows per warp and pass
@@ -91,7 +106,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
 
     if (p.nap > 0 && !p.rope_cos) {
         for (int pr = threadIdx.x; pr < p.nap; pr += blockDim.x)
-            s_inv[pr] = 1.0f / powf(p.theta, 2.0f * pr / static_cast<float>(HD));
+            s_inv[pr] = 1.0f / powf(p.theta, 2.0f * pr / static_cast<float>(QWEN ? p.freq_denom : HD));
         __syncthreads();
     }
     int it = 0;
@@ -112,7 +127,9 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     c = p.rope_cos[ti];
                     s = p.rope_sin[ti];
                 } else {
-                    const int pos = (p.pos_offset ? p.pos_offset[b] : p.pos0) + t;
+                    const int pos = (QWEN && p.mrope_pos)
+                                        ? p.mrope_pos[((long long)b * 3 + mrope_axis(pr, p.sec1, p.sec2)) * p.seq + t]
+                                        : (p.pos_offset ? p.pos_offset[b] : p.pos0) + t;
                     sincosf(static_cast<float>(pos) * s_inv[pr], &s, &c);
                 }
                 s_cos[tl * (HD / 2) + pr] = c;
@@ -134,7 +151,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
             const uint16_t* src = nullptr;
             uint16_t* dst = nullptr;
             const uint16_t* weight = nullptr;
-            bool rope = false;
+            bool rope = false, norm = true;
             if (valid) {
                 if (r < rows_q) {
                     src = dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
@@ -151,6 +168,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     src = p.v_src ? p.v_src + b * p.vs_stride_b + t * p.vs_stride_t + (long long)h * HD
                                   : p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
                     dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
+                    norm = !(QWEN && p.v_copy);
                 }
             }
             float lo[8], hi[8];
@@ -167,7 +185,9 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
 #pragma unroll
             for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float rms_inv = rsqrtf(ss / static_cast<float>(HD) + p.eps);
-            if (weight) {
+            if (!norm) {
+                // appended as it is
+            } else if (weight) {
                 float wl[8], wh[8];
                 unpack8(*reinterpret_cast<const uint4*>(weight + li * 8), wl);
                 unpack8(*reinterpret_cast<const uint4*>(weight + HD / 2 + li * 8), wh);
@@ -183,7 +203,24 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                     hi[e] = bf16_rne(hi[e] * rms_inv);
                 }
             }
-            if (rope) {
+            if (QWEN && p.rot_half != HD / 2) {
+                // Pairs (f, f + rot_half) both sit in the row's first half, rot_half / 8 lanes apart: the
+                // partner's values come by shuffle (every lane takes part; only the rotary lanes update).
+                const int dl = p.rot_half >> 3;
+                const bool mine = rope && li < 2 * dl;
+                const bool first = (li & dl) == 0;
+                const float* tc = s_cos + tl * (HD / 2);
+                const float* ts = s_sin + tl * (HD / 2);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float other = __shfl_xor_sync(0xffffffffu, lo[e], dl);
+                    const int pr = (li & (dl - 1)) * 8 + e;
+                    if (mine && pr < p.nap) {
+                        const float c = tc[pr], s = ts[pr];
+                        lo[e] = first ? lo[e] * c - other * s : other * s + lo[e] * c;
+                    }
+                }
+            } else if (rope) {
                 const float* tc = s_cos + tl * (HD / 2);
                 const float* ts = s_sin + tl * (HD / 2);
 #pragma unroll

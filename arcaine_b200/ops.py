@@ -391,7 +391,8 @@ def qkv_prepare(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optiona
                 q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
                 eps: float = 1e-6, theta: float = 10000.0, partial_rotary_factor: float = 1.0,
                 rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
-                pos_offset=None, v_from_k: bool = False) -> None:
+                pos_offset=None, v_from_k: bool = False, rotary_dim: Optional[int] = None,
+                mrope_positions: Optional[torch.Tensor] = None, mrope_section=None, v_copy: bool = False) -> None:
     """RMSNorm (+ RoPE) of the projected Q / K rows, unit-RMS norm of V and the KV-cache append, one launch.
 
     q: (B, S, nq, hd) or (S, nq, hd), rewritten in place.  k, v: (B, S, nkv, hd) projections.  K and V go to
@@ -400,6 +401,11 @@ def qkv_prepare(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optiona
     (full-attention layers, src/modeling/diffusion_gemma/attention.cpp:587-595).  ``pos_offset``: the position
     of the first token, an int or a device int32 tensor (B,); defaults to ``past_len``.  With ``rope_cos`` /
     ``rope_sin`` (S, n_active_pairs) or (B, S, n_active_pairs) f32 the angles are read, otherwise computed.
+
+    Qwen3.5 form (qwen35_apply_mrope, src/modeling/qwen3_5/kernels.hpp:576-617): ``rotary_dim`` rotates pairs
+    (f, f + rotary_dim/2) with frequency exponent 2f / rotary_dim; ``mrope_positions`` (B, 3, S) or (3, S) int32
+    with ``mrope_section`` (three ints) gives each frequency the position of its axis; ``v_copy`` appends V
+    without a norm.
     """
     ref = q if q is not None else k
     if ref is None:
@@ -454,6 +460,18 @@ def qkv_prepare(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optiona
     else:
         P.pos0 = past_len if pos_offset is None else int(pos_offset)
     P.theta, P.eps = float(theta), float(eps)
+    if rotary_dim is not None:
+        P.rot_half, P.freq_denom, P.n_active_pairs = rotary_dim // 2, rotary_dim, rotary_dim // 2
+    if mrope_positions is not None:
+        _require(mrope_positions, torch.int32, "mrope_positions")
+        if not mrope_positions.is_contiguous() or mrope_positions.numel() != B * 3 * S:
+            raise ValueError("mrope_positions must be a contiguous (B, 3, S) int32 tensor")
+        if mrope_section is None or len(mrope_section) != 3:
+            raise ValueError("Qwen3.5 MRoPE needs three sections")
+        P.mrope_positions = mrope_positions.data_ptr()
+        for i in range(3):
+            P.mrope_section[i] = int(mrope_section[i])
+    P.v_copy = 1 if v_copy else 0
     _lib.check(_lib.load().arc_qkv_prepare(C.byref(P), _stream_ptr(ref)), "arc_qkv_prepare")
 
 

@@ -257,6 +257,16 @@ typedef struct arc_qkv_prepare_params {
     int32_t pos0;             /* position of the first token when pos_offset is NULL */
     float theta;
     float eps;
+    /* Qwen3.5 form (qwen35_apply_mrope, src/modeling/qwen3_5/kernels.hpp:576-617; call site
+     * src/modeling/qwen3_5/operators.hpp:127-140).  All zero / NULL = the form described above. */
+    int32_t rot_half;         /* distance between the two values of a rotation pair; 0 = hd / 2.  Otherwise
+                               * a power of two, >= 8 and <= hd / 4 (pairs (f, f + rotary_dim / 2)) */
+    int32_t freq_denom;       /* denominator of the frequency exponent 2 f / denom; 0 = hd (Qwen3.5: rotary_dim) */
+    const int32_t* mrope_positions; /* device int32 (batch, 3, seq): position of every token on the temporal /
+                               * height / width axis; NULL = one position per token (pos_offset / pos0) */
+    int32_t mrope_section[3]; /* frequency f takes axis a in {1, 2} when a <= f < 3 * section[a] and f % 3 == a,
+                               * else axis 0 */
+    int32_t v_copy;           /* 1: V rows are appended as they are (no unit-RMS norm) */
 } arc_qkv_prepare_params;
 
 int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream);

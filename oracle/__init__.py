@@ -62,6 +62,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_mul_sigmoid_inplace.argtypes = [vp, vp, c.c_size_t]
         L.oracle_norm_rope.restype = None
         L.oracle_norm_rope.argtypes = [vp, c.c_longlong, vp, c.c_longlong, vp, i32, i32, i32, i32, i32, f32, f32, vp, vp]
+        L.oracle_mrope.restype = None
+        L.oracle_mrope.argtypes = [vp, vp, i32, i32, i32, i32, f32, vp]
         L.oracle_sdpa_f32.restype = i32
         L.oracle_sdpa_f32.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                       f32, vp, i64, vp, vp, vp]
@@ -152,6 +154,17 @@ def norm_rope(x: torch.Tensor, weight: Optional[torch.Tensor], *, eps: float, n_
                            theta, eps,
                            _ptr(cos) if cos is not None else None, _ptr(sin) if sin is not None else None)
     return bits_to_bf16(out).reshape(x.shape)
+
+
+def mrope(x: torch.Tensor, positions, rotary_dim: int, theta: float, sections) -> torch.Tensor:
+    """Qwen3.5 multi-axis RoPE of x (tokens, heads, head_dim) bf16 with positions (3, tokens); a new tensor."""
+    tokens, heads, hd = x.shape
+    xb = np.ascontiguousarray(_bits(x)).reshape(-1).copy()
+    pos = np.ascontiguousarray(np.asarray(positions), dtype=np.int32)
+    sec = np.ascontiguousarray(np.asarray(sections), dtype=np.int32)
+    assert pos.shape == (3, tokens) and sec.shape == (3,)
+    lib().oracle_mrope(_ptr(xb), _ptr(pos), tokens, heads, hd, rotary_dim, theta, _ptr(sec))
+    return bits_to_bf16(xb).reshape(x.shape)
 
 
 def sdpa_f32(q, k, v, *, scale: float, mask_type: int = MASK_NONE, window: int = INT_MAX,

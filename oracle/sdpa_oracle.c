@@ -190,6 +190,38 @@ ORACLE_API void oracle_norm_rope(const uint16_t* src, long long src_stride_t, ui
     }
 }
 
+/* ---- Qwen3.5 multi-axis RoPE : src/modeling/qwen3_5/kernels.hpp:576-617 ----
+ * In place on (tokens, heads, head_dim) rows: pairs (f, f + rotary_dim/2), f < rotary_dim/2,
+ * angle = positions[axis(f)][token] / theta^(2 f / rotary_dim), where a frequency takes axis
+ * a in {1, 2} when a <= f < 3 * sections[a] and f % 3 == a, else axis 0.  positions is
+ * (3, tokens). */
+static int mrope_axis(int frequency, const int* sections) {
+    for (int axis = 1; axis <= 2; ++axis) {
+        int limit = sections[axis] * 3;
+        if (frequency >= axis && frequency < limit && frequency % 3 == axis) return axis;
+    }
+    return 0;
+}
+
+ORACLE_API void oracle_mrope(uint16_t* x, const int32_t* positions, int tokens, int heads, int head_dim,
+                             int rotary_dim, float theta, const int* sections) {
+    const int half = rotary_dim / 2;
+    for (int t = 0; t < tokens; ++t)
+        for (int h = 0; h < heads; ++h) {
+            uint16_t* row = x + ((size_t)t * heads + h) * head_dim;
+            for (int f = 0; f < half; ++f) {
+                int axis = mrope_axis(f, sections);
+                int position = positions[(size_t)axis * tokens + t];
+                float inv = 1.0f / powf(theta, 2.0f * (float)f / (float)rotary_dim);
+                float angle = (float)position * inv;
+                float c = cosf(angle), sn = sinf(angle);
+                float x0 = b2f(row[f]), x1 = b2f(row[f + half]);
+                row[f] = f2b(x0 * c - x1 * sn);
+                row[f + half] = f2b(x0 * sn + x1 * c);
+            }
+        }
+}
+
 /* ---- grading oracle: fp32-softmax SDPA ------------------------------------
  * O = softmax(scale * Q K^T + mask) V on the bf16-valued inputs, with GQA
  * kv_head = q_head / (nq / nkv) (src/common/layers/attention_layout.hpp:37-52,

@@ -55,6 +55,7 @@ def test_struct_layouts_match_the_header():
             first = names[0].split()[-1]
             fields.append(first)
             fields += [n.strip() for n in names[1:]]
+        fields = [re.sub(r"\[\d+\]$", "", f) for f in fields]  # fixed-size array members
         assert fields == [f[0] for f in cls._fields_], cname
 
 

@@ -233,3 +233,27 @@ def test_preprocess_fixtures():
     q_len, kv_len, past, window = (int(v) for v in z["blockmask_params"])
     m = oracle.fill_causal_mask_with_block_ids(z["blockmask_ids"], q_len, kv_len, past, window)
     assert np.array_equal(np.isneginf(m), z["blockmask_hidden"])
+
+
+def test_mrope_restatement_matches_torch():
+    """qwen35_apply_mrope (src/modeling/qwen3_5/kernels.hpp:576-617) against a torch formulation."""
+    tokens, heads, hd, rd, theta, sec = 9, 3, 256, 64, 1e6, (11, 11, 10)
+    x = seeded_bf16(tokens, heads, hd, seed=77)
+    g = torch.Generator().manual_seed(78)
+    pos = torch.randint(0, 500, (3, tokens), generator=g, dtype=torch.int32)
+    got = oracle.mrope(x, pos.numpy(), rd, theta, sec)
+    half = rd // 2
+    f = torch.arange(half)
+    axis = torch.zeros(half, dtype=torch.long)
+    for a in (1, 2):
+        axis[(f >= a) & (f < sec[a] * 3) & (f % 3 == a)] = a
+    inv = 1.0 / torch.pow(torch.tensor(theta), 2.0 * f.float() / rd)
+    ang = pos.float()[axis, :].T * inv[None, :]             # (tokens, half)
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    xf = x.float()
+    want = xf.clone()
+    want[..., :half] = xf[..., :half] * c - xf[..., half:rd] * s
+    want[..., half:rd] = xf[..., :half] * s + xf[..., half:rd] * c
+    want = want.bfloat16().float()
+    assert ((got.float() - want).abs() <= want.abs() * 2.0 ** -7 + 2e-6).all()
+    assert torch.equal(got[..., rd:], x[..., rd:])          # the tail of every row is untouched

@@ -126,3 +126,35 @@ def test_against_committed_fixtures(ops):
         xd = x.cuda()
         ops.fused_norm_rope_inplace(xd, w.cuda(), offset, 10000.0, 2.0 * nap / hd, 1e-6)
         close_bf16(xd, want, name)
+
+
+@pytest.mark.parametrize("hd,rd", [(256, 64), (128, 32), (256, 128), (512, 64)])
+def test_qwen35_form_norm_mrope_and_plain_v_append(ops, hd, rd):
+    """Qwen3.5 layer call (src/modeling/qwen3_5/operators.hpp:127-140): q/k RMSNorm with weights, multi-axis
+    RoPE on the first rotary_dim values of every row (pairs rotary_dim/2 apart), K and V appended to the
+    cache, V as it is."""
+    B, seq, nq, nkv, past, cap, theta, sec = 2, 37, 6, 2, 11, 64, 1e6, (11, 11, 10)
+    q, k, v = seeded_bf16(B, seq, nq, hd, seed=51), seeded_bf16(B, seq, nkv, hd, seed=52), seeded_bf16(B, seq, nkv, hd, seed=53)
+    qw = (seeded_bf16(hd, seed=54).float() * 0.1 + 1.0).bfloat16()
+    kw = (seeded_bf16(hd, seed=55).float() * 0.1 + 1.0).bfloat16()
+    g = torch.Generator().manual_seed(56)
+    pos = torch.randint(0, 300, (B, 3, seq), generator=g, dtype=torch.int32)
+    kc = torch.zeros(B, cap, nkv, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qd = q.cuda()
+    ops.qkv_prepare(qd, k.cuda(), v.cuda(), k_cache=kc, v_cache=vc, past_len=past, q_weight=qw.cuda(), k_weight=kw.cuda(),
+                    eps=1e-6, theta=theta, rotary_dim=rd, mrope_positions=pos.cuda(), mrope_section=sec, v_copy=True)
+    for b in range(B):
+        want_q = oracle.mrope(oracle.norm_rope(q[b], qw, eps=1e-6), pos[b].numpy(), rd, theta, sec)
+        want_k = oracle.mrope(oracle.norm_rope(k[b], kw, eps=1e-6), pos[b].numpy(), rd, theta, sec)
+        close_bf16(qd[b], want_q, f"Q{b}")
+        close_bf16(kc[b, past:past + seq], want_k, f"K{b}")
+        assert torch.equal(vc[b, past:past + seq].cpu(), v[b]), "V must be appended bit for bit"
+    assert not kc[:, :past].any() and not vc[:, past + seq:].any()
+
+
+def test_qwen35_form_rejects_unsupported_rotary_dim(ops):
+    from arcaine_b200 import _lib
+    x = torch.zeros(4, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.ArcError):
+        ops.qkv_prepare(x, None, None, rotary_dim=96)   # pairs 48 apart: not a power of two
