@@ -663,6 +663,12 @@ def cpu_sample(workload: str, reps: int = 1):
     """Time the CPU port on a bounded sample of the workload.  Returns (value, unit, cores, sample text)."""
     import torch
     import oracle
+    # all the cores this process may run on, whatever OMP_NUM_THREADS a launcher set
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    oracle.set_num_threads(avail)
     cores = oracle.num_threads()
     if workload in ("prefill_window", "canvas"):
         if workload == "prefill_window":

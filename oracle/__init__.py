@@ -52,6 +52,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_float_to_bf16.restype = c.c_uint16
         L.oracle_float_to_bf16.argtypes = [f32]
         L.oracle_num_threads.restype = i32
+        L.oracle_set_num_threads.restype = None
+        L.oracle_set_num_threads.argtypes = [i32]
         L.oracle_lcg_fill.restype = None
         L.oracle_lcg_fill.argtypes = [vp, c.c_size_t, c.POINTER(c.c_uint32)]
         L.oracle_fill_causal_mask.restype = None
@@ -82,6 +84,10 @@ def lib() -> ctypes.CDLL:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().oracle_set_num_threads(int(n))
 
 
 def _bits(t) -> np.ndarray:

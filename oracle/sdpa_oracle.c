@@ -56,6 +56,16 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* The launcher of a multi-process run pins OMP_NUM_THREADS to 1; the timed CPU baseline asks for
+ * the host's cores explicitly. */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ---- bench input recipe : src/bench/qwen35_attention_bench.cpp:86-94 ----- */
 /* LCG state*1664525+1013904223; x = (((state>>16)&1023) - 512)/1024 -> bf16.
  * `state` is carried across calls so Q, K, V can be filled in that order. */
