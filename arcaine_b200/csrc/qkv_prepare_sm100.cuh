@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
     __shared__ float s_cos2[2][1024];  // [round parity][token in round][pair]: one barrier per round is enough
     __shared__ float s_sin2[2][1024];
     __shared__ float s_inv[HD / 2];    // rotation frequencies, computed once
+    __shared__ int s_bt[2][2 * 16];     // [round parity][token in round] -> (batch index, token in sequence)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPR;     // which of the warp's rows
@@ -114,6 +115,15 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
         const int tk0 = rd * tpc;
         float* s_cos = s_cos2[it & 1];
         float* s_sin = s_sin2[it & 1];
+        // The tokens of this round, split into (sequence, position) once: the row loop below would
+        // otherwise divide per row.
+        int* s_tok = s_bt[it & 1];
+        if (threadIdx.x < tpc && tk0 + (int)threadIdx.x < tokens) {
+            const int tk = tk0 + threadIdx.x;
+            const int b = tk / p.seq;
+            s_tok[2 * threadIdx.x] = b;
+            s_tok[2 * threadIdx.x + 1] = tk - b * p.seq;
+        }
         if (p.nap > 0) {
             for (int idx = threadIdx.x; idx < tpc * p.nap; idx += blockDim.x) {
                 const int tl = idx / p.nap, pr = idx - tl * p.nap;
@@ -135,19 +145,20 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
                 s_cos[tl * (HD / 2) + pr] = c;
                 s_sin[tl * (HD / 2) + pr] = s;
             }
-            // Readers of this buffer two rounds ago finished before every thread reached the
-            // previous round's barrier, so one barrier per round orders both directions.
-            __syncthreads();
         }
+        // Readers of these buffers two rounds ago finished before every thread reached the previous
+        // round's barrier, so one barrier per round orders both directions.
+        __syncthreads();
+        const float inv_rows = 1.0f / static_cast<float>(rows);
         const int slots = tpc * rows;  // (token in round, row) pairs of this round
         for (int r0 = warp * RPW; r0 < slots; r0 += 8 * RPW) {
             const int slot = r0 + sub;
-            const int tl = slot / rows;
+            const int tl = static_cast<int>((static_cast<float>(slot) + 0.5f) * inv_rows);  // exact: slot < 2^20
             const int r = slot - tl * rows;
             const int tk = tk0 + tl;
             const bool valid = slot < slots && tk < tokens;
-            const int b = valid ? tk / p.seq : 0;
-            const int t = valid ? tk - b * p.seq : 0;
+            const int b = valid ? s_tok[2 * tl] : 0;
+            const int t = valid ? s_tok[2 * tl + 1] : 0;
             const uint16_t* src = nullptr;
             uint16_t* dst = nullptr;
             const uint16_t* weight = nullptr;
