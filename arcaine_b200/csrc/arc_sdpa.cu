@@ -215,10 +215,10 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.mask_type = p->mask_type;
     kp.window = p->window;
     kp.num_splits = plan.splits;
-#ifdef ARC_PREFILL_TRACE
-    kp.trace = reinterpret_cast<long long*>(p->out_lse);  // debug builds reuse the lse slot as the trace buffer
-    kp.out_lse = nullptr;
-#endif
+    kp.group = p->nq / p->nkv;
+    kp.group_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == kp.group) kp.group_shift = sh;
 
     // Head dim 128: two query tiles per CTA (prefill_pair_sm100.cuh) when that is the faster way to cover
     // the tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair overrides the choice (for A/B measurements).
@@ -228,18 +228,24 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             if (!e) return 0;
             return std::strcmp(e, "pair") == 0 ? 2 : (std::strcmp(e, "single") == 0 ? 1 : 0);
         }();
-        const long long pair_tiles = (long long)((p->seq + 255) / 256) * p->nq * p->batch;
-        // Measured: a pair of tiles costs 1.87 single tiles.  Tiles come in waves of one per SM, so the
+        // A CTA takes two 128-row tiles: the same tokens of two heads of one KV group when the group
+        // size is even (both tiles then see exactly the same key blocks), else 256 tokens of one head.
+        const bool head_pair = ((p->nq / p->nkv) & 1) == 0;
+        const long long pair_tiles = head_pair ? (long long)plan.q_tiles * (p->nq / 2) * p->batch
+                                               : (long long)((p->seq + 255) / 256) * p->nq * p->batch;
+        // Measured: a pair of tiles costs 1.7 single tiles.  Tiles come in waves of one per SM, so the
         // kernel with the cheaper whole number of waves wins (512 pair tiles on 148 SMs are 4 waves,
         // the same rows as 1024 single tiles are 7: the single-tile kernel is then faster).
         const long long single_tiles = (long long)plan.q_tiles * p->nq * p->batch;
         const long long sms = ds->sm_count;
-        const double cost_pair = 1.87 * (double)((pair_tiles + sms - 1) / sms);
+        const double cost_pair = 1.7 * (double)((pair_tiles + sms - 1) / sms);
         const double cost_single = (double)((single_tiles + sms - 1) / sms);
         const bool use_pair = forced == 2 || (forced == 0 && cost_pair <= cost_single);
         if (use_pair) {
             if (pair_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
-            kp.q_tiles = (p->seq + 255) / 256;
+            kp.head_pair = head_pair ? 1 : 0;
+            kp.cur_heads = head_pair ? p->nq / 2 : p->nq;
+            kp.q_tiles = head_pair ? plan.q_tiles : (p->seq + 255) / 256;
             kp.total_tiles = (int)pair_tiles;
             const unsigned ctas = (unsigned)(pair_tiles < ds->sm_count ? pair_tiles : ds->sm_count);
             if (kp.gate) sdpa_prefill_pair_kernel<true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
@@ -252,6 +258,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
 
     // Persistent grid: one CTA per SM (fewer if there are fewer tiles), tiles dealt round-robin.
     kp.q_tiles = plan.q_tiles;
+    kp.cur_heads = p->nq;
+    kp.head_pair = 0;
     const long long total_tiles = (long long)plan.q_tiles * p->nq * p->batch * plan.splits;
     if (total_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
     kp.total_tiles = (int)total_tiles;

@@ -7,18 +7,28 @@
 // columns), one Q buffer in shared memory.  The two pipelines share the K and V rings, which
 // one producer thread fills by TMA, so every key block is fetched once for 256 rows.
 //
+// Sixteen warps in four groups with register budgets of their own (setmaxnreg):
+//   warps 0-3 / 4-7   softmax of tile A / B: a thread takes its row's 128 scores out of tensor
+//                     memory ONCE, masks them in registers where the block needs it, takes the
+//                     maximum, exponentiates and writes P (bf16) back over the scores;
+//   warps 8-11        epilogue: once a tile's last O += P V has landed they read the accumulator
+//                     out, normalise, gate and store it, while the softmax warps are already
+//                     working on the next tile's first key block;
+//   warps 12-15       TMA producer of K / V, MMA issuer of A, MMA issuer of B, TMA producer of Q
+//                     (one thread each).
+//
 // The pipelines run out of phase: while the softmax warps of A turn S_A(j) into P_A(j), the
 // tensor pipe works for B (O_B += P_B V, S_B = Q_B K^T), and the other way round.  Left alone
 // they fall into step (both wait for the tensor pipe, then both fight for the ex2 unit), so the
 // phase is enforced: the softmax warps take turns at the exponentials, block by block, through
-// a pair of mbarriers.  Per block
-// and pipeline the issuer does   wait P(j);  O += P(j) V(j);  S(j+1) = Q K(j+1)^T   — P is
-// written over S, so the next scores can only follow the P V that reads them, and both come
-// from one thread, in order.  The two issuers sit on different instruction schedulers.
+// a pair of mbarriers.  Per block and pipeline the issuer does
+//   wait P(j);  O += P(j) V(j);  S(j+1) = Q K(j+1)^T
+// — P is written over S, so the next scores can only follow the P V that reads them, and both
+// come from one thread, in order.
 //
-// Masking, lazy rescaling, probabilities as bf16 over the score columns, bounded waits and
-// the device status word are as in the single-tile kernel (prefill_sm100.cuh), which keeps
-// head dim 256, additive masks and key-range splits.
+// Lazy rescaling, probabilities as bf16 over the score columns, bounded waits and the device
+// status word are as in the single-tile kernel (prefill_sm100.cuh), which keeps head dim 256,
+// additive masks and key-range splits.
 #pragma once
 #include "prefill_sm100.cuh"
 
@@ -37,67 +47,104 @@ struct PairCfg {
     static constexpr int COL_S = 0;    // + 128 * pipeline
     static constexpr int COL_O = 256;  // + 128 * pipeline
     // q_full[2] q_empty[2] k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] then per pipeline:
-    // s_full p_full pv_done o_full o_empty turn
+    // s_full p_full o_full o_empty turn fin
     static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 12;
-    static constexpr int SMEM_BYTES = (2 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + 1024;
-    static constexpr int SOFTMAX_WARPS = 8;  // four per pipeline
-    static constexpr int PRODUCER_WARP = 8;
-    static constexpr int ISSUER_WARP = 9;    // + pipeline
-    static constexpr int THREADS = 32 * 11;
-    static constexpr int MAX_REGS = 168;     // 65536 registers over 12 allocated warps
+    static constexpr int FIN_FLOATS = 2 * 2 * 128 * 2;  // [tile parity][pipeline][row] (row sum, row maximum)
+    static constexpr int SMEM_BYTES = (2 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + FIN_FLOATS * 4 + 1024;
+    static constexpr int SOFTMAX_WARPS = 8;   // four per pipeline
+    static constexpr int EPILOGUE_WARP = 8;   // four warps
+    static constexpr int PRODUCER_WARP = 12;
+    static constexpr int ISSUER_WARP = 13;    // + pipeline
+    static constexpr int Q_PRODUCER_WARP = 15;
+    static constexpr int THREADS = 32 * 16;
+    // The budgets may only redistribute what the CTA holds at launch (threads x the per-thread
+    // count the launch bound gives, 128 for 512 threads): a group that asks for more waits for ever.
+    static constexpr int REGS_SOFTMAX = 192;
+    static constexpr int REGS_EPILOGUE = 80;
+    static constexpr int REGS_CONTROL = 48;
+    static constexpr int LAUNCH_REGS = (65536 / THREADS) & ~7;
+    static_assert((SOFTMAX_WARPS * REGS_SOFTMAX + 4 * REGS_EPILOGUE + 4 * REGS_CONTROL) * 32 <= THREADS * LAUNCH_REGS,
+                  "register budgets exceed what the CTA holds at launch");
 };
 
-// One unit of work: 256 query tokens of one head; per tile the key blocks [lo, hi) it can see.
+// One unit of work: two 128-row tiles, and per tile the key blocks [lo, hi) it can see.  With an
+// even number of query heads per KV head the tiles are the same 128 tokens of two heads of one KV
+// group: both walk exactly the same key blocks, so neither pipeline ever idles while the other
+// works on a block only it can see.  Otherwise they are 256 consecutive tokens of one head.
 struct PairWork {
-    int q0, h, b, kvh;
+    int q0[2], h[2];
+    int b, kvh;
     int lo[2], hi[2];
     int ulo, uhi;  // union of the two ranges (contiguous)
     bool live[2];  // the tile has rows below seq
     // Selected without dynamic indexing, so the struct stays in registers.
+    __device__ __forceinline__ int q0_of(int s) const { return s ? q0[1] : q0[0]; }
+    __device__ __forceinline__ int h_of(int s) const { return s ? h[1] : h[0]; }
     __device__ __forceinline__ int lo_of(int s) const { return s ? lo[1] : lo[0]; }
     __device__ __forceinline__ int hi_of(int s) const { return s ? hi[1] : hi[0]; }
     __device__ __forceinline__ bool live_of(int s) const { return s ? live[1] : live[0]; }
 };
 
+// Key blocks [lo, hi) a 128-row tile starting at token qs can see.
+__device__ __forceinline__ void tile_blocks(const PrefillParams& p, int qs, int& blk_lo, int& blk_hi) {
+    const int off = p.kv_len - p.seq;
+    blk_lo = 0;
+    blk_hi = (p.kv_len + PairCfg::BN - 1) / PairCfg::BN;
+    if (p.mask_type == 3) {
+        const int q_last = min(qs + PairCfg::BM - 1, p.seq - 1);
+        const int last_key = min(p.kv_len - 1, q_last + off);
+        blk_hi = last_key >= 0 ? last_key / PairCfg::BN + 1 : 0;
+        if (p.window > 0 && p.window != 0x7fffffff) blk_lo = max(0, qs + off - p.window + 1) / PairCfg::BN;
+    }
+    if (blk_hi < blk_lo) blk_hi = blk_lo;
+}
+
+// Every role runs this once per unit, from code that has long left the instruction caches by
+// then, so it is kept short: one division at most, and nothing computed twice.
 __device__ __forceinline__ PairWork decode_pair(const PrefillParams& p, const TileCursor& cur) {
     PairWork t;
-    t.h = cur.h;
     t.b = cur.z;
-    t.kvh = t.h / (p.nq / p.nkv);
-    t.q0 = cur.qt * 2 * PairCfg::BM;
-    const int off = p.kv_len - p.seq;
-    const bool causal = (p.mask_type == 3);
-    const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
-    t.ulo = 0x7fffffff;
-    t.uhi = 0;
+    if (p.head_pair) {
+        t.h[0] = cur.h * 2;
+        t.h[1] = t.h[0] + 1;
+        t.q0[0] = t.q0[1] = cur.qt * PairCfg::BM;
+        t.kvh = p.group_shift >= 0 ? (t.h[0] >> p.group_shift) : t.h[0] / p.group;
+        t.live[0] = t.live[1] = true;  // the tile list only holds tiles with rows
+        tile_blocks(p, t.q0[0], t.lo[0], t.hi[0]);
+        t.lo[1] = t.ulo = t.lo[0];
+        t.hi[1] = t.uhi = t.hi[0];
+    } else {
+        t.h[0] = t.h[1] = cur.h;
+        t.q0[0] = cur.qt * 2 * PairCfg::BM;
+        t.q0[1] = t.q0[0] + PairCfg::BM;
+        t.kvh = p.group_shift >= 0 ? (cur.h >> p.group_shift) : cur.h / p.group;
+        t.live[0] = true;
+        t.live[1] = t.q0[1] < p.seq;
+        tile_blocks(p, t.q0[0], t.lo[0], t.hi[0]);
+        t.lo[1] = t.hi[1] = 0;
+        if (t.live[1]) tile_blocks(p, t.q0[1], t.lo[1], t.hi[1]);
+        t.ulo = 0x7fffffff;
+        t.uhi = 0;
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
-        const int qs = t.q0 + s * PairCfg::BM;
-        t.live[s] = qs < p.seq;
-        int blk_lo = 0, blk_hi = 0;
-        if (t.live[s]) {
-            blk_hi = (p.kv_len + PairCfg::BN - 1) / PairCfg::BN;
-            if (causal) {
-                const int q_last = min(qs + PairCfg::BM - 1, p.seq - 1);
-                const int last_key = min(p.kv_len - 1, q_last + off);
-                blk_hi = last_key >= 0 ? last_key / PairCfg::BN + 1 : 0;
-                if (windowed) blk_lo = max(0, qs + off - p.window + 1) / PairCfg::BN;
+        for (int s = 0; s < 2; ++s)
+            if (t.hi[s] > t.lo[s]) {
+                t.ulo = min(t.ulo, t.lo[s]);
+                t.uhi = max(t.uhi, t.hi[s]);
             }
-            if (blk_hi < blk_lo) blk_hi = blk_lo;
-        }
-        t.lo[s] = blk_lo;
-        t.hi[s] = blk_hi;
-        if (blk_hi > blk_lo) {
-            t.ulo = min(t.ulo, blk_lo);
-            t.uhi = max(t.uhi, blk_hi);
-        }
     }
     if (t.uhi == 0) t.ulo = 0;
     return t;
 }
 
-template <bool GATE>  // the gated epilogue is an instance of its own: 13 KB of code the common kernel does not carry
-__global__ void __maxnreg__(PairCfg::MAX_REGS)
+// Scores of keys outside the row's visible span [lo, hi) become -inf, in registers.
+__device__ __forceinline__ void mask_chunk(uint32_t (&v)[32], int key0, const RowMask& rm) {
+    const uint32_t lo_rel = static_cast<uint32_t>(rm.lo - key0), span = static_cast<uint32_t>(rm.hi - rm.lo);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = (static_cast<uint32_t>(e) - lo_rel < span) ? v[e] : 0xff800000u;  // lo <= key < hi
+}
+
+template <bool GATE>  // the gated epilogue is an instance of its own: code the common kernel does not carry
+__global__ void __launch_bounds__(PairCfg::THREADS, 1)
     sdpa_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
     using C = PairCfg;
@@ -118,12 +165,13 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
     uint64_t* v_empty = v_full + VS; // [VS] two arrivals
     uint64_t* s_full = v_empty + VS; // [2] per pipeline from here on
     uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 2;  // one phase per key block: O += P V of that block has completed
-    uint64_t* o_full = pv_done + 2;  // one phase per tile
-    uint64_t* o_empty = o_full + 2;  // one phase per tile: the softmax warps have read O out
+    uint64_t* o_full = p_full + 2;   // one phase per tile: the tile's last O += P V has completed
+    uint64_t* o_empty = o_full + 2;  // one phase per tile: the epilogue warps have read O out
     uint64_t* turn = o_empty + 2;    // one phase per union key block: the pipeline's softmax warps are past it
+    uint64_t* fin = turn + 2;        // one phase per tile: the softmax warps have published row sums and maxima
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
+    float2* fin_vals = reinterpret_cast<float2*>(tmem_slot + 4);  // [tile parity 2][pipeline 2][row 128] (row sum, row maximum)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -131,9 +179,6 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
     if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
     __syncthreads();
     if (*abort_slot) return;
-#ifdef ARC_TRACE_CTAS
-    const long long ck0 = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
@@ -141,10 +186,10 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
             mbar_init(&q_empty[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], 128);
-            mbar_init(&pv_done[s], 1);
             mbar_init(&o_full[s], 1);
             mbar_init(&o_empty[s], 128);
             mbar_init(&turn[s], 128);
+            mbar_init(&fin[s], 128);
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
@@ -165,185 +210,292 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp == C::PRODUCER_WARP) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            prefetch_tensormap(&tm_q);
-            prefetch_tensormap(&tm_k);
-            prefetch_tensormap(&tm_v);
-            int gk = 0, gv = 0;        // key blocks loaded into each ring so far
-            int tq[2] = {0, 0};        // tiles with key blocks loaded so far, per pipeline
-            bool ok = true;
-            TileCursor cur;
-            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
-                const PairWork pw = decode_pair(p, cur);
+    if (warp >= C::PRODUCER_WARP) {
+        reg_dealloc<C::REGS_CONTROL>();
+        if (warp == C::PRODUCER_WARP) {
+            // -------------------------------------------------------------- TMA producer of K and V
+            if (lane == 0) {
+                prefetch_tensormap(&tm_k);
+                prefetch_tensormap(&tm_v);
+                int gk = 0, gv = 0;        // key blocks loaded into each ring so far
+                bool ok = true;
+                TileCursor cur;
+                for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+                    const PairWork pw = decode_pair(p, cur);
+                    // K stays at most two blocks ahead of V; both rings fill in the order of use.
+                    const int n = pw.uhi - pw.ulo;
+                    int uk = 0, uv = 0;
+                    while (ok && (uk < n || uv < n)) {
+                        if (uk < n && (uk <= uv + 1 || uv >= n)) {
+                            const int st = gk % KS;
+                            if (gk >= KS && !mbar_wait<1>(&k_empty[st], ((gk / KS) - 1) & 1)) {
+                                report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u);
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
 #pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    if (pw.hi[s] == pw.lo[s]) continue;
-                    if (tq[s] > 0 && !mbar_wait(&q_empty[s], (tq[s] - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x300u + s);
-                        ok = false;
+                            for (int c = 0; c < C::CH; ++c)
+                                tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, pw.kvh,
+                                            (pw.ulo + uk) * C::BN, pw.b);
+                            ++uk;
+                            ++gk;
+                        } else {
+                            const int st = gv % VS;
+                            if (gv >= VS && !mbar_wait<1>(&v_empty[st], ((gv / VS) - 1) & 1)) {
+                                report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u);
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
+#pragma unroll
+                            for (int c = 0; c < C::CH; ++c)
+                                tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, pw.kvh,
+                                            (pw.ulo + uv) * C::BN, pw.b);
+                            ++uv;
+                            ++gv;
+                        }
+                    }
+                }
+            }
+        } else if (warp == C::Q_PRODUCER_WARP) {
+            // -------------------------------------------------------------- TMA producer of Q
+            // A thread of its own: the next unit's Q tiles are requested the moment the current tiles'
+            // last scores are out, whatever the K / V producer is waiting for at that time.
+            if (lane == 0) {
+                prefetch_tensormap(&tm_q);
+                int tq0 = 0, tq1 = 0;  // tiles with key blocks loaded so far, per pipeline
+                bool ok = true;
+                TileCursor cur;
+                for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+                    const PairWork pw = decode_pair(p, cur);
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) {
+                        if (pw.hi[s] == pw.lo[s]) continue;
+                        int& tq = s ? tq1 : tq0;
+                        if (tq > 0 && !mbar_wait<1>(&q_empty[s], (tq - 1) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_EMPTY, 0x300u + s);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
+#pragma unroll
+                        for (int c = 0; c < C::CH; ++c)
+                            tma_load_4d(sQ + s * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_q, &q_full[s], c * 64, pw.h[s],
+                                        pw.q0[s], pw.b);
+                        ++tq;
+                    }
+                    // The unit after this one: its Q rows (one 256-byte piece per token, far apart in
+                    // memory) are asked into L2 now, a whole unit ahead of the load that needs them.
+                    TileCursor nx = cur;
+                    nx.advance(p);
+                    if (ok && nx.w < p.total_tiles) {
+                        const PairWork pn = decode_pair(p, nx);
+#pragma unroll
+                        for (int s = 0; s < 2; ++s) {
+                            if (pn.hi[s] == pn.lo[s]) continue;
+#pragma unroll
+                            for (int c = 0; c < C::CH; ++c) tma_prefetch_4d(&tm_q, c * 64, pn.h[s], pn.q0[s], pn.b);
+                        }
+                    }
+                }
+            }
+        } else if (warp <= C::ISSUER_WARP + 1) {
+            // -------------------------------------------------------------- MMA issuer of one pipeline
+            if (lane == 0) {
+                const int s = warp - C::ISSUER_WARP;
+                constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
+                constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
+                const uint32_t tS = tmem_base + C::COL_S + s * 128;
+                const uint32_t tO = tmem_base + C::COL_O + s * 128;
+                // Descriptors are built once; per MMA only the start-address field (bytes >> 4, in
+                // the low word) moves, by a compile-time constant.
+                const uint64_t dQ = make_smem_desc_sw128(smem_u32(sQ + s * C::TILE_BYTES), 16, 1024);
+                const uint64_t dK = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
+                const uint64_t dV = make_smem_desc_sw128(smem_u32(sV), C::CHUNK_BYTES, 1024);
+                static_assert(KS == 2 && VS == 2 && HD == 128, "ring arithmetic assumes two stages and head dim 128");
+                int gu = 0;  // union key blocks passed so far (ring position, same in both issuers)
+                int g = 0;   // key blocks of this pipeline issued so far
+                int tq = 0;  // tiles of this pipeline with key blocks so far
+                bool ok = true;
+                // S = Q K(j)^T for ring position r; releases the K stage.  For a block this pipeline does
+                // not use, only the release (once the stage has been filled, so arrivals stay in step).
+                auto scores = [&](int r, bool active, bool last) -> bool {
+                    if (!mbar_wait<1>(&k_full[r % KS], (r / KS) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_K, r);
+                        return false;
+                    }
+                    if (!active) {
+                        mbar_arrive(&k_empty[r % KS]);
+                        return true;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t dKs = dK + (uint64_t)((r & 1) * (C::TILE_BYTES >> 4));
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim columns
+                        umma_ss(tS, dQ + o, dKs + o, IDESC_QK, kk > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&s_full[s]);
+                    umma_commit(&k_empty[r % KS]);
+                    if (last) umma_commit(&q_empty[s]);
+                    return true;
+                };
+                TileCursor cur;
+                for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+                    const PairWork pw = decode_pair(p, cur);
+                    const int lo = pw.lo_of(s), hi = pw.hi_of(s);
+                    if (pw.uhi == pw.ulo) continue;
+                    if (hi > lo && !mbar_wait<1>(&q_full[s], tq & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_Q, tq);
                         break;
                     }
-                    mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
-#pragma unroll
-                    for (int c = 0; c < C::CH; ++c)
-                        tma_load_4d(sQ + s * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_q, &q_full[s], c * 64, pw.h,
-                                    pw.q0 + s * C::BM, pw.b);
-                    ++tq[s];
-                }
-                // K stays at most two blocks ahead of V; both rings fill in the order of use.
-                const int n = pw.uhi - pw.ulo;
-                int uk = 0, uv = 0;
-                while (ok && (uk < n || uv < n)) {
-                    if (uk < n && (uk <= uv + 1 || uv >= n)) {
-                        const int st = gk % KS;
-                        if (gk >= KS && !mbar_wait(&k_empty[st], ((gk / KS) - 1) & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_EMPTY, 0x100u);
+                    // Position j: O += P(j) V(j), then S(j+1).  The loop starts one position early, so that
+                    // the tile's first scores come out of the same (single) place in the code.
+                    for (int j = pw.ulo - 1; ok && j < pw.uhi; ++j) {
+                        const bool act = j >= lo && j < hi;
+                        if (j >= pw.ulo && !mbar_wait<1>(&v_full[gu % VS], (gu / VS) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_V, gu);
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(&k_full[st], C::TILE_BYTES);
+                        if (j >= pw.ulo)                        if (j < pw.ulo) {
+                            // nothing to accumulate yet
+                        } else if (act) {
+                            if (!mbar_wait<1>(&p_full[s], g & 1)) {
+                                report_fault(p.fault, FAULT_WAIT_P, g);
+                                ok = false;
+                                break;
+                            }
+                            if (j == lo && tq > 0 && !mbar_wait<1>(&o_empty[s], (tq - 1) & 1)) {
+                                report_fault(p.fault, FAULT_WAIT_O, 0x100u + tq);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            // P from tensor memory: each 32-key chunk keeps its 16 bf16x2 columns at the
+                            // start of its own 32 score columns.  V is MN-major: 64-element head-dim
+                            // chunks 16 KB apart, 8-key groups 1024 bytes apart; 16 keys = 2048 bytes.
+                            const uint64_t dVs = dV + (uint64_t)((gu & 1) * (C::TILE_BYTES >> 4));
 #pragma unroll
-                        for (int c = 0; c < C::CH; ++c)
-                            tma_load_4d(sK + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_k, &k_full[st], c * 64, pw.kvh,
-                                        (pw.ulo + uk) * C::BN, pw.b);
-                        ++uk;
-                        ++gk;
-                    } else {
-                        const int st = gv % VS;
-                        if (gv >= VS && !mbar_wait(&v_empty[st], ((gv / VS) - 1) & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_EMPTY, 0x200u);
-                            ok = false;
-                            break;
+                            for (int kk = 0; kk < 8; ++kk)
+                                umma_ts(tO, tS + (kk >> 1) * 32 + (kk & 1) * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
+                                        (j > lo || kk > 0) ? 1u : 0u);
+                            umma_commit(&v_empty[gu % VS]);
+                            if (j + 1 == hi) umma_commit(&o_full[s]);
+                            ++g;
+                        } else {
+                            mbar_arrive(&v_empty[gu % VS]);
                         }
-                        mbar_arrive_expect_tx(&v_full[st], C::TILE_BYTES);
-#pragma unroll
-                        for (int c = 0; c < C::CH; ++c)
-                            tma_load_4d(sV + st * C::TILE_BYTES + c * C::CHUNK_BYTES, &tm_v, &v_full[st], c * 64, pw.kvh,
-                                        (pw.ulo + uv) * C::BN, pw.b);
-                        ++uv;
-                        ++gv;
+                        if (j >= pw.ulo) ++gu;  // ring position of block j + 1 from here on
+                        // S(j+1): over the P just consumed, behind the MMAs that read it
+                        if (j + 1 < pw.uhi) {
+                            const bool act1 = j + 1 >= lo && j + 1 < hi;
+                            ok = scores(gu, act1, act1 && j + 2 == hi);
+                        }
                     }
+                    if (hi > lo) ++tq;
                 }
             }
         }
-    } else if (warp == C::ISSUER_WARP || warp == C::ISSUER_WARP + 1) {
-        // ------------------------------------------------------------------ MMA issuer of one pipeline
-        if (lane == 0) {
-            const int s = warp - C::ISSUER_WARP;
-            constexpr uint32_t IDESC_QK = make_idesc_bf16(128, 128, false);
-            constexpr uint32_t IDESC_PV = make_idesc_bf16(128, HD, true);
-            const uint32_t tS = tmem_base + C::COL_S + s * 128;
-            const uint32_t tO = tmem_base + C::COL_O + s * 128;
-            // Every operand descriptor the thread will ever need, built once (only the address
-            // field, bytes >> 4 in the low word, differs): per MMA nothing is left to compute.
-            const uint64_t dQ = make_smem_desc_sw128(smem_u32(sQ + s * C::TILE_BYTES), 16, 1024);
-            const uint64_t dK = make_smem_desc_sw128(smem_u32(sK), 16, 1024);
-            const uint64_t dV = make_smem_desc_sw128(smem_u32(sV), C::CHUNK_BYTES, 1024);
-            uint64_t aQ[8], bK[8], bV[8];  // K and V: stage 0; the other stage is TILE_BYTES further
-            uint32_t aP[8];
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t o = ((kk >> 2) * C::CHUNK_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim columns
-                aQ[kk] = dQ + o;
-                bK[kk] = dK + o;
-                // 16 keys of V: 8-key groups 1024 bytes apart; of P: 8 packed columns, each 32-key
-                // chunk at the start of its own 32 score columns
-                bV[kk] = dV + ((kk * 2048) >> 4);
-                aP[kk] = tS + (kk >> 1) * 32 + (kk & 1) * 8;
-            }
-            static_assert(KS == 2 && VS == 2 && HD == 128, "descriptor tables assume two stages and head dim 128");
-            int gu = 0;  // union key blocks passed so far (ring position, same in both issuers)
-            int g = 0;   // key blocks of this pipeline issued so far
-            int tq = 0;  // tiles of this pipeline with key blocks so far
-            bool ok = true;
-            // S = Q K(j)^T for ring position r; releases the K stage.  For a block this pipeline does
-            // not use, only the release (once the stage has been filled, so arrivals stay in step).
-            auto scores = [&](int r, bool active, bool last) -> bool {
-                if (!mbar_wait(&k_full[r % KS], (r / KS) & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_K, r);
-                    return false;
+    } else if (warp >= C::EPILOGUE_WARP) {
+        // ------------------------------------------------------------------ epilogue
+        // Thread = query row (TMEM lane); tiles A and B of every unit in turn.  The accumulator is
+        // released as soon as it is in registers, normally before the next tile's first P is ready.
+        reg_dealloc<C::REGS_EPILOGUE>();
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+        int tq0 = 0, tq1 = 0;  // tiles with key blocks so far, per pipeline
+        bool ok = true;
+        uint32_t wa[32];
+        TileCursor cur;
+        for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
+            const PairWork pw = decode_pair(p, cur);
+#pragma unroll 1
+            for (int s = 0; s < 2 && ok; ++s) {
+                const int t = pw.q0_of(s) + r;
+                const bool store = pw.live_of(s) && t < p.seq;
+                const long long row = ((long long)pw.b * p.seq + t) * p.nq + pw.h_of(s);
+                const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h_of(s) * HD;
+                if (pw.hi_of(s) == pw.lo_of(s)) {
+                    // Nothing visible for this tile: zero output.
+                    if (store) {
+                        uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
+                        for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
+                    }
+                    continue;
                 }
-                if (!active) {
-                    mbar_arrive(&k_empty[r % KS]);
-                    return true;
-                }
-                tc_fence_after_sync();
-                {
-                    uint64_t b[8];
-                    const uint64_t stage = (uint64_t)((r & 1) * (C::TILE_BYTES >> 4));
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk) b[kk] = bK[kk] + stage;
-                    umma_ss_x8(tS, aQ, b, IDESC_QK, 0u);
-                }
-                umma_commit(&s_full[s]);
-                umma_commit(&k_empty[r % KS]);
-                if (last) umma_commit(&q_empty[s]);
-                return true;
-            };
-            TileCursor cur;
-            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
-                const PairWork pw = decode_pair(p, cur);
-                const int lo = pw.lo_of(s), hi = pw.hi_of(s);
-                if (pw.uhi == pw.ulo) continue;
-                if (hi > lo && !mbar_wait(&q_full[s], tq & 1)) {
-                    report_fault(p.fault, FAULT_WAIT_Q, tq);
+                const int tq = s ? tq1 : tq0;
+                if (!mbar_wait_relaxed_warp<2>(&fin[s], tq & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_FULL, 0x500u + s);
+                    ok = false;
                     break;
                 }
-                // Position j: O += P(j) V(j), then S(j+1).  The loop starts one position early, so that
-                // the tile's first scores come out of the same (single) place in the code.
-                for (int j = pw.ulo - 1; ok && j < pw.uhi; ++j) {
-                    const bool act = j >= lo && j < hi;
-                    if (j >= pw.ulo && !mbar_wait(&v_full[gu % VS], (gu / VS) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_V, gu);
-                        ok = false;
-                        break;
-                    }
-                    if (j < pw.ulo) {
-                        // nothing to accumulate yet
-                    } else if (act) {
-                        if (!mbar_wait(&p_full[s], g & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_P, g);
-                            ok = false;
-                            break;
-                        }
-                        if (j == lo && tq > 0 && !mbar_wait(&o_empty[s], (tq - 1) & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_O, 0x100u + tq);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        // P from tensor memory: each 32-key chunk keeps its 16 bf16x2 columns at the
-                        // start of its own 32 score columns.  V is MN-major: 64-element head-dim
-                        // chunks 16 KB apart, 8-key groups 1024 bytes apart.
-                        {
-                            uint64_t b[8];
-                            const uint64_t stage = (uint64_t)((gu & 1) * (C::TILE_BYTES >> 4));
+                const float2 fv = fin_vals[((tq & 1) * 2 + s) * 128 + r];
+                const float row_l = fv.x, row_m = fv.y;
+                if (!mbar_wait_relaxed_warp<2>(&o_full[s], tq & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_O, tq);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                if (s) ++tq1; else ++tq0;
+                const float inv = row_l > 0.f ? 1.0f / row_l : 0.f;
+                const uint32_t tO = tmem_base + lane_sel + C::COL_O + s * 128;
+                uint16_t* dst = p.out + eoff;
+                const uint16_t* gp = GATE ? p.gate + eoff : nullptr;
+                const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
 #pragma unroll
-                            for (int kk = 0; kk < 8; ++kk) b[kk] = bV[kk] + stage;
-                            umma_ts_x8(tO, aP, b, IDESC_PV, j > lo ? 1u : 0u);
-                        }
-                        umma_commit(&v_empty[gu % VS]);
-                        umma_commit(&pv_done[s]);
-                        if (j + 1 == hi) umma_commit(&o_full[s]);
-                        ++g;
-                    } else {
-                        mbar_arrive(&v_empty[gu % VS]);
+                for (int c = 0; c < HD / 32; ++c) {
+                    tmem_ld32(tO + c * 32, wa);
+                    tmem_wait_ld();
+                    if (c + 1 == HD / 32) {
+                        // O is in registers: the next tile may overwrite the accumulator.
+                        tc_fence_before_sync();
+                        mbar_arrive(&o_empty[s]);
                     }
-                    if (j >= pw.ulo) ++gu;  // ring position of block j + 1 from here on
-                    // S(j+1): over the P just consumed, behind the MMAs that read it
-                    if (j + 1 < pw.uhi) {
-                        const bool act1 = j + 1 >= lo && j + 1 < hi;
-                        ok = scores(gu, act1, act1 && j + 2 == hi);
+                    if (store) {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {  // 16 values = 32 bytes per round
+                            uint32_t w8[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                w8[u] = pack_bf16x2(__uint_as_float(wa[i * 16 + 2 * u]) * inv, __uint_as_float(wa[i * 16 + 2 * u + 1]) * inv);
+                            if (GATE) {
+                                // bf16(attention) * sigmoid(gate): the rounding order of the two-launch form
+                                const uint4 g0 = *reinterpret_cast<const uint4*>(gp + c * 32 + i * 16);
+                                const uint4 g1 = *reinterpret_cast<const uint4*>(gp + c * 32 + i * 16 + 8);
+                                const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const float a0 = __uint_as_float(w8[u] << 16), a1 = __uint_as_float(w8[u] & 0xffff0000u);
+                                    const float g0f = __uint_as_float(gw[u] << 16), g1f = __uint_as_float(gw[u] & 0xffff0000u);
+                                    w8[u] = pack_bf16x2(a0 * (1.0f / (1.0f + __expf(-g0f))), a1 * (1.0f / (1.0f + __expf(-g1f))));
+                                }
+                            }
+                            uint16_t* q = dst + c * 32 + i * 16;
+                            if (wide) {
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(w8[0]),
+                                             "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]), "r"(w8[6]), "r"(w8[7])
+                                             : "memory");
+                            } else {
+                                *reinterpret_cast<uint4*>(q) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+                                *reinterpret_cast<uint4*>(q + 8) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+                            }
+                        }
                     }
                 }
-                if (hi > lo) ++tq;
+                if (store && p.out_lse)
+                    p.out_lse[row] = row_l > 0.f ? (row_m + fast_log2(row_l)) * 0.6931471805599453f : -CUDART_INF_F;
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax / epilogue
-        // Warps 0-3 serve tile A, warps 4-7 tile B; a thread owns one query row.
+        // ------------------------------------------------------------------ softmax
+        // Warps 0-3 serve tile A, warps 4-7 tile B; a thread owns one query row and takes its 128
+        // scores of a block out of tensor memory once.
+        reg_alloc<C::REGS_SOFTMAX>();
         const int s = warp >> 2;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
@@ -358,45 +510,13 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
         int g = 0, tq = 0;  // key blocks and tiles (with key blocks) of this pipeline so far
         int gu = 0;         // union key blocks of the CTA so far (the same count in both pipelines)
         bool ok = true;
-        uint32_t wa[32], wb[32];
-#ifdef ARC_PREFILL_TRACE
-        int tpos = 0;
-#ifndef ARC_TR_THREAD
-#define ARC_TR_THREAD 0
-#endif
-#ifndef ARC_TR_CTA
-#define ARC_TR_CTA 0
-#endif
-#ifndef ARC_TR_MIN
-#define ARC_TR_MIN 0
-#endif
-        const bool tr = p.trace && blockIdx.x == ARC_TR_CTA && threadIdx.x == ARC_TR_THREAD;
-#ifndef ARC_TR_SKIP
-#define ARC_TR_SKIP 0
-#endif
-#define ARC_TP(code) do { if (tr && tpos < 200 && (code) >= ARC_TR_MIN && tq >= ARC_TR_SKIP) { p.trace[2 * tpos] = (code); p.trace[2 * tpos + 1] = clock64(); ++tpos; } } while (0)
-#else
-#define ARC_TP(code) do { } while (0)
-#endif
+        uint32_t s0[32], s1[32], s2[32], s3[32];  // the row's 128 scores of the current block
 
         TileCursor cur;
         for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
             const PairWork pw = decode_pair(p, cur);
-            if (pw.uhi == pw.ulo) {
-                // No key block for either tile: zero output for the rows that exist.
-                const int t = pw.q0 + s * C::BM + r;
-                if (pw.live_of(s) && t < p.seq) {
-                    const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h * HD;
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
-                    for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.out_lse) p.out_lse[((long long)pw.b * p.seq + t) * p.nq + pw.h] = -CUDART_INF_F;
-                }
-                continue;
-            }
-            const int t = pw.q0 + s * C::BM + r;
-            const long long row = ((long long)pw.b * p.seq + t) * p.nq + pw.h;
-            const long long eoff = pw.b * p.o_stride_b + t * p.o_stride_t + (long long)pw.h * HD;
-            const bool store = pw.live_of(s) && t < p.seq;
+            if (pw.uhi == pw.ulo) continue;
+            const int t = pw.q0_of(s) + r;
             const int lo = pw.lo_of(s), hi = pw.hi_of(s);
             int row_lo = 0, row_hi = p.kv_len;  // visible keys [row_lo, row_hi)
             if (causal) {
@@ -409,235 +529,128 @@ __global__ void __maxnreg__(PairCfg::MAX_REGS)
 
             float m = -CUDART_INF_F;  // running max, log2 domain, possibly stale by <= 8
             float l = 0.f;            // row sum
-            ARC_TP(1000 + hi - lo);
             // Both pipelines walk every key block of the pair, used or not, and take turns at the
-            // exponentials (the two warps of a scheduler share one ex2 unit): A's block u goes after
-            // B's block u - 1, B's block u after A's block u.  That keeps the pipelines half a
-            // period apart, so that one computes while the tensor pipe works for the other.
+            // exponentials: A's block u goes after B's block u - 1, B's block u after A's block u.
+            // That keeps the pipelines half a period apart, so that one computes while the tensor
+            // pipe works for the other.
             for (int j = pw.ulo; j < pw.uhi; ++j, ++gu) {
                 const bool act = j >= lo && j < hi;
                 const int kc = j * C::BN;
-                bool full = false;
                 float m_eff = 0.f;
+                // 32-key chunks no row of the warp can see (bit c set) are neither reduced nor exponentiated
+                uint32_t none = 0u;
                 if (act) {
-                    ARC_TP(10);
-                    if (!mbar_wait_warp(&s_full[s], g & 1)) {
+                    if (!mbar_wait_warp<3>(&s_full[s], g & 1)) {
                         report_fault(p.fault, FAULT_WAIT_S, g);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    ARC_TP(11);
                     // Every key of the block visible to every row of the warp (seven blocks in nine
-                    // with a 1024-key window): no per-element tests and no per-chunk votes.
-                    full = __all_sync(0xffffffffu, rm.lo <= kc && kc + C::BN <= rm.hi);
-                    // Pass 1: row maximum of the block, 64 keys per round.  The loops are kept rolled and
-                    // the masked form has a single body: the kernel has to stay small enough for the
-                    // instruction cache, and the masked blocks (window edge, diagonal) are the cold code.
-                    float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                    float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-                    if (full) {
-                        // the hot path: the next chunk loads while one is reduced
-                        tmem_ld32(tS, wa);
-                        tmem_ld32(tS + 32, wb);
+                    // with a 1024-key window): no element tests at all.
+                    const bool full = __all_sync(0xffffffffu, rm.lo <= kc && kc + C::BN <= rm.hi);
+                    for (;;) {
+                        tmem_ld32(tS, s0);
+                        tmem_ld32(tS + 32, s1);
+                        tmem_ld32(tS + 64, s2);
+                        tmem_ld32(tS + 96, s3);
                         tmem_wait_ld();
-                        chunk_max<0>(wa, mr, sl, kc, rm);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_max<0>(wb, mr, sl, kc + 32, rm);
-                        tmem_ld32(tS + 96, wb);
-                        tmem_wait_ld();
-                        chunk_max<0>(wa, mr, sl, kc + 64, rm);
-                        tmem_ld32(tS, wa);  // first chunk again, for the exponentials
-                        chunk_max<0>(wb, mr, sl, kc + 96, rm);
-                    } else {
-                        // cold path (window edge, diagonal): one 32-key chunk at a time through one body
-#pragma unroll 1
-                        for (int c = 0; c < 128; c += 32) {
-                            if (chunk_class(kc + c, rm) == 2) continue;
-                            tmem_ld32(tS + c, wb);
-                            tmem_wait_ld();
-                            chunk_max<1>(wb, ms, sl, kc + c, rm);
+                        float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                        if (full) {
+                            chunk_max<0>(s0, mr, sl, kc, rm);
+                            chunk_max<0>(s1, mr, sl, kc, rm);
+                            chunk_max<0>(s2, mr, sl, kc, rm);
+                            chunk_max<0>(s3, mr, sl, kc, rm);
+                        } else {
+                            // window edge, diagonal, ragged end: per chunk either whole, mixed (scores of
+                            // keys outside the row's span become -inf in registers) or out of sight
+                            none = 0u;
+                            int cls = chunk_class(kc, rm);
+                            if (cls == 1) mask_chunk(s0, kc, rm);
+                            if (cls == 2) none |= 1u; else chunk_max<0>(s0, mr, sl, kc, rm);
+                            cls = chunk_class(kc + 32, rm);
+                            if (cls == 1) mask_chunk(s1, kc + 32, rm);
+                            if (cls == 2) none |= 2u; else chunk_max<0>(s1, mr, sl, kc, rm);
+                            cls = chunk_class(kc + 64, rm);
+                            if (cls == 1) mask_chunk(s2, kc + 64, rm);
+                            if (cls == 2) none |= 4u; else chunk_max<0>(s2, mr, sl, kc, rm);
+                            cls = chunk_class(kc + 96, rm);
+                            if (cls == 1) mask_chunk(s3, kc + 96, rm);
+                            if (cls == 2) none |= 8u; else chunk_max<0>(s3, mr, sl, kc, rm);
                         }
-                        tmem_ld32(tS, wa);
-                    }
-                    const float bm = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
-                                           fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
-                    const float m_new = fmaxf(m, bm);
-                    if (j == lo) {
-                        m = m_new;
-                    } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
-                        // Rare: some row's maximum grows by more than 2^8.  Once O += P V of the previous
-                        // block has landed, rescale those rows of O in tensor memory.
-                        const bool need = m_new > m + 8.0f;
-                        const float alpha = !need ? 1.0f : (m_new == -CUDART_INF_F ? 1.0f : fast_exp2(m - m_new));
-                        tmem_wait_ld();
-                        if (!mbar_wait_warp(&pv_done[s], (g - 1) & 1)) {
-                            report_fault(p.fault, FAULT_WAIT_O, g);
-                            ok = false;
+                        const float m_new = fmaxf(m, fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl);
+                        if (j == lo) {
+                            m = m_new;
                             break;
                         }
-                        tc_fence_after_sync();
+                        const bool need = m_new > m + 8.0f;
+                        if (!__any_sync(0xffffffffu, need)) break;
+                        // Rare: some row's maximum grows by more than 2^8.  O += P V of the previous block
+                        // has landed (these scores were issued behind it): rescale those rows of O in
+                        // tensor memory, then take the scores again (their registers were the scratch).
+                        const float alpha = need ? fast_exp2(m - m_new) : 1.0f;
 #pragma unroll 1
                         for (int c = 0; c < HD / 32; ++c) {
-                            tmem_ld32(tO + c * 32, wb);
+                            tmem_ld32(tO + c * 32, s0);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) wb[e] = __float_as_uint(__uint_as_float(wb[e]) * alpha);
-                            tmem_st32(tO + c * 32, wb);
+                            for (int e = 0; e < 32; ++e) s0[e] = __float_as_uint(__uint_as_float(s0[e]) * alpha);
+                            tmem_st32(tO + c * 32, s0);
                         }
                         tmem_wait_st();
                         l *= alpha;
                         if (need) m = m_new;
-                        tmem_ld32(tS, wa);
                     }
                     m_eff = (m == -CUDART_INF_F) ? 0.f : m;
-                    tmem_ld32(tS + 32, wb);
-                    ARC_TP(12);
                 }
                 // my turn?
                 {
                     uint64_t* other = &turn[s ^ 1];
                     const bool must = (s == 1) || gu > 0;
                     const uint32_t parity = (uint32_t)((s == 1) ? gu : gu - 1) & 1u;
-                    if (must && !mbar_wait_warp(other, parity)) {
+                    if (must && !mbar_wait_warp<3>(other, parity)) {
                         report_fault(p.fault, FAULT_WAIT_FULL, 0x400u + s);
                         ok = false;
                         break;
                     }
                 }
                 if (act) {
-                    ARC_TP(14);
-                    // Pass 2: probabilities as bf16, each 32-key chunk over the first 16 of its own 32
-                    // score columns; row sum in fp32.  Rolled, 64 keys per round.
+                    // Probabilities as bf16, each 32-key chunk over the first 16 of its own 32 score
+                    // columns; row sum in fp32.
                     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                     uint32_t pk[16];
-                    if (full) {
-                        // unrolled on purpose: rolling these four saves 5 KB of code but costs 3 %
-                        tmem_wait_ld();
-                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc, rm);
-                        tmem_st16(tS, pk);
-                        tmem_ld32(tS + 64, wa);
-                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 32, rm);
-                        tmem_st16(tS + 32, pk);
-                        tmem_ld32(tS + 96, wb);
-                        tmem_wait_ld();
-                        chunk_exp<0>(wa, pk, ls4, sl, m_eff, kc + 64, rm);
-                        tmem_st16(tS + 64, pk);
-                        chunk_exp<0>(wb, pk, ls4, sl, m_eff, kc + 96, rm);
-                        tmem_st16(tS + 96, pk);
-                    } else {
-                        tmem_wait_ld();
-#pragma unroll 1
-                        for (int c = 0; c < 128; c += 32) {
-                            if (chunk_class(kc + c, rm) == 2) {
+                    auto zero_pk = [&]() {
 #pragma unroll
-                                for (int e = 0; e < 16; ++e) pk[e] = 0u;
-                            } else {
-                                tmem_ld32(tS + c, wb);
-                                tmem_wait_ld();
-                                chunk_exp<1>(wb, pk, ls4, sl, m_eff, kc + c, rm);
-                            }
-                            tmem_st16(tS + c, pk);
-                        }
-                    }
+                        for (int e = 0; e < 16; ++e) pk[e] = 0u;
+                    };
+                    if (none & 1u) zero_pk(); else chunk_exp<0>(s0, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS, pk);
+                    if (none & 2u) zero_pk(); else chunk_exp<0>(s1, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS + 32, pk);
+                    if (none & 4u) zero_pk(); else chunk_exp<0>(s2, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS + 64, pk);
+                    if (none & 8u) zero_pk(); else chunk_exp<0>(s3, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS + 96, pk);
                     l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(&p_full[s]);
                     ++g;
-                    ARC_TP(13);
                 }
                 mbar_arrive(&turn[s]);
                 if (act && j + 1 == hi) {
-                    // The tile's last key block is on its way: read the accumulator out now, before the
-                    // turns for the blocks only the other tile still uses.
-                    ARC_TP(20);
-
-                    // Accumulator out: one thread writes the 256 contiguous bytes of its row.
-                    if (!mbar_wait_warp(&o_full[s], tq & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_O, tq);
-                        ok = false;
-                        break;
-                    }
+                    // The tile's last key block is on its way: hand the row sum and maximum to the
+                    // epilogue warps and go on with the next tile.
+                    fin_vals[((tq & 1) * 2 + s) * 128 + r] = make_float2(l, m);
+                    mbar_arrive(&fin[s]);
                     ++tq;
-                    tc_fence_after_sync();
-                    ARC_TP(21);
-                    const float inv = l > 0.f ? 1.0f / l : 0.f;
-                    const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
-                    uint16_t* dst = p.out + eoff;
-                    const uint16_t* gp = GATE ? p.gate + eoff : nullptr;
-                    const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
-                    auto store_chunk = [&](const uint32_t (&w)[32], int c) {
-                        if (store) {
-        #pragma unroll
-                            for (int e = 0; e < 32; e += 16) {
-                                uint32_t ov[8];
-        #pragma unroll
-                                for (int hh = 0; hh < 2; ++hh) {
-                                    float o[8];
-        #pragma unroll
-                                    for (int u = 0; u < 8; ++u) o[u] = __uint_as_float(w[e + hh * 8 + u]) * inv;
-                                    if (gp) {
-                                        const uint4 gv = *reinterpret_cast<const uint4*>(gp + c * 32 + e + hh * 8);
-                                        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-        #pragma unroll
-                                        for (int u = 0; u < 8; ++u) {
-                                            const float gf = bf16_bits_to_f32(static_cast<uint16_t>(gw[u >> 1] >> ((u & 1) * 16)));
-                                            const float sig = 1.0f / (1.0f + __expf(-gf));
-                                            o[u] = bf16_round(o[u]) * sig;
-                                        }
-                                    }
-        #pragma unroll
-                                    for (int u = 0; u < 4; ++u) ov[hh * 4 + u] = pack_bf16x2(o[2 * u], o[2 * u + 1]);
-                                }
-                                uint16_t* q = dst + c * 32 + e;
-                                if (wide) {
-                                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(ov[0]),
-                                                 "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]), "r"(ov[6]), "r"(ov[7])
-                                                 : "memory");
-                                } else {
-                                    *reinterpret_cast<uint4*>(q) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                                    *reinterpret_cast<uint4*>(q + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
-                                }
-                            }
-                        }
-                    };
-                    // two 32-column chunks per round: their loads are in flight together
-        #pragma unroll 1
-                    for (int c = 0; c < HD / 32; c += 2) {
-                        tmem_ld32(tO + c * 32, wa);
-                        tmem_ld32(tO + c * 32 + 32, wb);
-                        tmem_wait_ld();
-                        if (c + 2 == HD / 32) {
-                            // O is in registers: the next tile may overwrite the accumulator.
-                            tc_fence_before_sync();
-                            mbar_arrive(&o_empty[s]);
-                        }
-                        store_chunk(wa, c);
-                        store_chunk(wb, c + 1);
-                    }
-                    if (store && p.out_lse) p.out_lse[row] = lse;
-                    ARC_TP(22);
                 }
-            }
-            if (!ok) break;
-            if (hi == lo) {
-                // Nothing visible for this tile: zero output.
-                if (store) {
-                    uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
-                    for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-                    if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
-                }
-                continue;
             }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef ARC_TRACE_CTAS
-    if (threadIdx.x == 0 && p.trace) p.trace[800 + blockIdx.x] = clock64() - ck0;
-#endif
     if (warp == C::PRODUCER_WARP) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 

@@ -44,10 +44,11 @@ struct PrefillParams {
     int mask_type, window;
     int num_splits;
     int q_tiles;      // ceil(seq / 128)
-    int total_tiles;  // q_tiles * nq * batch * num_splits, dealt round-robin to the persistent CTAs
-#ifdef ARC_PREFILL_TRACE
-    long long* trace;  // debug builds only: per-block timestamps of CTA 0
-#endif
+    int total_tiles;  // q_tiles * cur_heads * batch * num_splits, dealt round-robin to the persistent CTAs
+    int cur_heads;    // head units the tile list walks: nq, or nq / 2 when a CTA takes two query heads at a time
+    int head_pair;    // prefill_pair_sm100.cuh: 1 = the CTA's two tiles are the same tokens of two heads of one KV group
+    int group;        // nq / nkv
+    int group_shift;  // log2(group) if it is a power of two, else -1
 };
 
 // One CTA per SM, persistent: it takes tiles (128 query tokens of one query head) round-robin
@@ -106,43 +107,6 @@ __device__ __forceinline__ float masked_score(uint32_t raw, float sl, int key, c
     return (key >= rm.lo && key < rm.hi) ? x : -CUDART_INF_F;
 }
 
-// 2^x for x <= ~100 without the special-function unit: split off the integer part with the
-// 1.5 * 2^23 rounding trick, a degree-3 minimax polynomial for 2^f on [-0.5, 0.5], and the
-// integer part added straight into the exponent field.  Inputs below -125 are clamped (the
-// result is then ~2^-125, which rounds to a bf16 of no consequence).
-__device__ __forceinline__ float poly_exp2(float x) {
-    x = fmaxf(x, -125.0f);
-    const float t = x + 12582912.0f;
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.0551716610789299f, 0.2426111251115799f);
-    p = fmaf(f, p, 0.6932609677314758f);
-    p = fmaf(f, p, 0.9999280571937561f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
-// The same for two values at once on the packed fp32 pipe.
-__device__ __forceinline__ void poly_exp2_x2(uint64_t x, float& r0, float& r1) {
-    float x0, x1;
-    unpack_f32x2(x, x0, x1);
-    x = pack_f32x2(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
-    const uint64_t t = add_f32x2(x, pack_f32x2(12582912.0f, 12582912.0f));
-    const uint64_t u = add_f32x2(t, pack_f32x2(-12582912.0f, -12582912.0f));
-    const uint64_t f = fma_f32x2(u, pack_f32x2(-1.0f, -1.0f), x);
-    uint64_t p = fma_f32x2(f, pack_f32x2(0.0551716610789299f, 0.0551716610789299f),
-                           pack_f32x2(0.2426111251115799f, 0.2426111251115799f));
-    p = fma_f32x2(f, p, pack_f32x2(0.6932609677314758f, 0.6932609677314758f));
-    p = fma_f32x2(f, p, pack_f32x2(0.9999280571937561f, 0.9999280571937561f));
-    float p0, p1, t0, t1;
-    unpack_f32x2(p, p0, p1);
-    unpack_f32x2(t, t0, t1);
-    r0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-    r1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
-}
-
-#ifndef ARC_POLY_MOD
-#define ARC_POLY_MOD 8  // one pair of scores in every ARC_POLY_MOD pairs takes the polynomial
-#endif
-
 // Maximum of one 32-column chunk, folded into four independent running maxima.
 template <int MODE>
 __device__ __forceinline__ void chunk_max(const uint32_t (&v)[32], float (&mx)[4], float sl, int key0,
@@ -169,55 +133,32 @@ template <int MODE>
 __device__ __forceinline__ void chunk_exp(const uint32_t (&v)[32], uint32_t (&pk)[16], float (&ls)[4], float sl,
                                           float m_eff, int key0, const RowMask& rm) {
     if constexpr (MODE == 0) {
-        // Every key visible: two scores per instruction on the packed fp32 pipe (scale and
-        // subtract the maximum with one fma.f32x2, accumulate the row sum with one add.f32x2),
-        // which leaves the issue port to the exponentials and to the MMA-issuing warp.
-        const uint64_t sl2 = pack_f32x2(sl, sl);
-        const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
-        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+        // Every key visible.  Plain fp32 instructions on purpose: measured on B200, a warp issues an
+        // fma.f32x2 / add.f32x2 only every ~8 clocks (the scalar forms every clock), about as often as
+        // an ex2.approx; both the packed forms and a polynomial 2^x on the FMA pipe for a share of
+        // the scores made the kernel slower.
+        const float nm = -m_eff;
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-            const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), sl2, nm2);
-            // A share of the exponentials is evaluated on the FMA pipe (degree-3 polynomial,
-            // relative error 7.5e-5, far below bf16 resolution): the quarter-rate ex2 unit is
-            // what bounds this loop.
-            float p0, p1;
-            if (((e >> 1) & (ARC_POLY_MOD - 1)) == 1) {
-                poly_exp2_x2(x, p0, p1);
-            } else {
-                float x0, x1;
-                unpack_f32x2(x, x0, x1);
-                p0 = fast_exp2(x0);
-                p1 = fast_exp2(x1);
-            }
-            acc[(e >> 1) & 3] = add_f32x2(acc[(e >> 1) & 3], pack_f32x2(p0, p1));
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[e]), sl, nm));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), sl, nm));
+            ls[e & 3] += p0;
+            ls[(e + 1) & 3] += p1;
             pk[e >> 1] = pack_bf16x2(p0, p1);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            float a, b;
-            unpack_f32x2(acc[u], a, b);
-            ls[u] += a + b;
         }
     } else if constexpr (MODE == 1) {
-        // Per-row span: the same packed arithmetic, plus one select per score (exp2(-inf) = 0).
-        const uint64_t sl2 = pack_f32x2(sl, sl);
-        const uint64_t nm2 = pack_f32x2(-m_eff, -m_eff);
+        // Per-row span: one select per score (exp2(-inf) = 0).
+        const float nm = -m_eff;
         const int lo_rel = rm.lo - key0, hi_rel = rm.hi - key0;  // visible: lo_rel <= e < hi_rel
-        uint64_t acc[2] = {0ull, 0ull};
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-            float x0, x1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])), sl2, nm2), x0, x1);
+            const float x0 = fmaf(__uint_as_float(v[e]), sl, nm), x1 = fmaf(__uint_as_float(v[e + 1]), sl, nm);
             const float p0 = fast_exp2((e >= lo_rel && e < hi_rel) ? x0 : -CUDART_INF_F);
             const float p1 = fast_exp2((e + 1 >= lo_rel && e + 1 < hi_rel) ? x1 : -CUDART_INF_F);
-            acc[(e >> 1) & 1] = add_f32x2(acc[(e >> 1) & 1], pack_f32x2(p0, p1));
+            ls[e & 3] += p0;
+            ls[(e + 1) & 3] += p1;
             pk[e >> 1] = pack_bf16x2(p0, p1);
         }
-        float a, b, c, d;
-        unpack_f32x2(acc[0], a, b);
-        unpack_f32x2(acc[1], c, d);
-        ls[0] += (a + b) + (c + d);
     } else {
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
@@ -280,7 +221,7 @@ struct TileWork {
     int my_lo, n_my;  // key blocks [my_lo, my_lo + n_my) of this tile and split
 };
 
-// Position of a persistent CTA in the launch's tile list: tile w = ((z * nq) + h) * q_tiles + qt,
+// Position of a persistent CTA in the launch's tile list: tile w = ((z * cur_heads) + h) * q_tiles + qt,
 // token tiles fastest (neighbouring CTAs share K/V blocks in L2), then query heads, then
 // z = batch * num_splits + split.  The cursor moves by gridDim.x tiles per step with carries
 // instead of dividing again.
@@ -291,13 +232,13 @@ struct TileCursor {
         w = blockIdx.x;
         qt = w % p.q_tiles;
         const int rest = w / p.q_tiles;
-        h = rest % p.nq;
-        z = rest / p.nq;
+        h = rest % p.cur_heads;
+        z = rest / p.cur_heads;
         const int step = gridDim.x;
         dqt = step % p.q_tiles;
         const int srest = step / p.q_tiles;
-        dh = srest % p.nq;
-        dz = srest / p.nq;
+        dh = srest % p.cur_heads;
+        dz = srest / p.cur_heads;
     }
     __device__ __forceinline__ void advance(const PrefillParams& p) {
         w += gridDim.x;
@@ -305,8 +246,8 @@ struct TileCursor {
         int carry = qt >= p.q_tiles ? 1 : 0;
         qt -= carry * p.q_tiles;
         h += dh + carry;
-        carry = h >= p.nq ? 1 : 0;
-        h -= carry * p.nq;
+        carry = h >= p.cur_heads ? 1 : 0;
+        h -= carry * p.cur_heads;
         z += dz + carry;
     }
 };
@@ -323,7 +264,7 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
         t.b = cur.z / p.num_splits;
         t.split = cur.z % p.num_splits;
     }
-    t.kvh = t.h / (p.nq / p.nkv);
+    t.kvh = p.group_shift >= 0 ? (t.h >> p.group_shift) : t.h / p.group;
     t.q0 = cur.qt * C::BM;
     const int off = p.kv_len - p.seq;
     const bool causal = (p.mask_type == 3);
@@ -576,13 +517,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
 
         int gb = 0, tc = 0;  // key blocks and non-empty tiles processed so far
         bool ok = true;
-#ifdef ARC_PREFILL_TRACE
-        int tpos = 0;
-        const bool tr = p.trace && blockIdx.x == 0 && threadIdx.x == 0;
-#define ARC_TR(code) do { if (tr && tpos < 200) { p.trace[2 * tpos] = (code); p.trace[2 * tpos + 1] = clock64(); ++tpos; } } while (0)
-#else
-#define ARC_TR(code) do { } while (0)
-#endif
         uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
 
         TileCursor cur;
@@ -650,7 +584,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 return true;
             };
 
-            ARC_TR(1000 + tw.n_my);  // tile start
             // Block 0: publish, meet, adopt the row maximum, fetch the scores.
             if (ok) ok = publish_max(0);
             pair_sync(quarter);
@@ -670,9 +603,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 // The next block's scores were computed one or two blocks ago: take their maximum
                 // now, so that the exchange through shared memory is hidden behind this block's
                 // exponentials.
-                ARC_TR(10);  // block start
                 if (ok && have_next) ok = publish_max(i + 1);
-                ARC_TR(11);  // next max published
                 if (ok) {
                     // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its
                     // own 32 score columns; row-sum share in fp32.
@@ -694,7 +625,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(&p_full[g % NSB]);
-                    ARC_TR(12);  // P arrived
                     if (have_next) {  // lands during the barrier below
                         tmem_ld32(tS0 + ((g + 1) % NSB) * 128, va);
                         tmem_ld32(tS0 + ((g + 1) % NSB) * 128 + 32, vb);
@@ -739,7 +669,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             xch_sum[kh * 128 + r] = l;
             pair_sync(quarter);
             l = xch_sum[r] + xch_sum[128 + r];
-            ARC_TR(20);  // waiting for O
             if (ok && !mbar_wait_warp(o_full, tc & 1)) {
                 report_fault(p.fault, FAULT_WAIT_O, tc);
                 ok = false;
@@ -747,7 +676,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             ++tc;
             if (!ok) continue;
             tc_fence_after_sync();
-            ARC_TR(21);  // O complete
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const float lse = l > 0.f ? (m + fast_log2(l)) * 0.6931471805599453f : -CUDART_INF_F;
             const bool store = t < p.seq;
@@ -780,7 +708,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
                     tmem_wait_ld();
-                    ARC_TR(23);  // O chunk in registers
                     if (c == OC / 32 - 1) {
                         tc_fence_before_sync();
                         mbar_arrive(o_empty);
@@ -821,7 +748,6 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 }
                 if (store && kh == 0 && p.out_lse) p.out_lse[row] = lse;
             }
-            ARC_TR(22);  // tile written
         }
     }
 

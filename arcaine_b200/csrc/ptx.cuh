@@ -43,6 +43,21 @@ __device__ __forceinline__ uint32_t lane_id() {
 }
 
 // ---------------------------------------------------------------------------
+// Register budget per warp group (four consecutive warps; every thread of the
+// group executes the same statement): a group that needs few registers hands
+// them back so that another can take more than the launch-time share.
+// ---------------------------------------------------------------------------
+template <int REGS>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+template <int REGS>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -82,6 +97,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same with a suspend-time hint: the hardware may keep the thread asleep, without issuing
+// anything, until the phase completes or about `hint_ns` have passed.  A waiting warp then takes
+// no issue slots from the warps of its scheduler that have work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Non-blocking: has the phase with the given parity completed?
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -100,26 +130,51 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // caller records a fault and unwinds.
 // The polling loop is one out-of-line function: waits are all over the kernels and their code
 // would otherwise be repeated at every site (the kernels have to fit the instruction cache).
+// GROUP gives warp groups that run under different register budgets (setmaxnreg) a copy each:
+// the assembler cannot place a function that is called from regions with different budgets.
+template <int GROUP>
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, long long limit_cycles) {
-    long long t0 = clock64();
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3FFu) == 0 && clock64() - t0 > limit_cycles) return false;
+    const long long t0 = clock64();
+    while (!mbar_try_wait_hint(bar, parity, 200000u)) {
+        if (clock64() - t0 > limit_cycles) return false;
     }
     return true;
 }
 
+template <int GROUP = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           long long limit_cycles = 2000000000LL) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, limit_cycles);
+    return mbar_wait_slow<GROUP>(bar, parity, limit_cycles);
+}
+
+// The same for waits that are long and not urgent (an epilogue waiting for a whole tile): the
+// thread sleeps between polls, so that it does not take issue slots from the warps that work.
+template <int GROUP>
+__device__ __noinline__ bool mbar_wait_relaxed_slow(uint64_t* bar, uint32_t parity, long long limit_cycles) {
+    long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(100);
+        if ((++spins & 0x3Fu) == 0 && clock64() - t0 > limit_cycles) return false;
+    }
+    return true;
+}
+
+template <int GROUP = 0>
+__device__ __forceinline__ bool mbar_wait_relaxed_warp(uint64_t* bar, uint32_t parity,
+                                                       long long limit_cycles = 2000000000LL) {
+    bool ok = mbar_try_wait(bar, parity);
+    if (!ok) ok = mbar_wait_relaxed_slow<GROUP>(bar, parity, limit_cycles);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // Same, with a warp-uniform answer (every lane polls; all must succeed), so the
 // warp-collective tcgen05 / ldmatrix instructions that follow never see a
 // partially exited warp.
+template <int GROUP = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+    return __all_sync(0xffffffffu, mbar_wait<GROUP>(bar, parity));
 }
 
 // ---------------------------------------------------------------------------
@@ -138,6 +193,15 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
         " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
+}
+
+// The same tile brought into L2 only (no shared-memory destination, nothing to wait for): a later
+// load of it then completes with L2 latency instead of DRAM latency.
+__device__ __forceinline__ void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
 }
 
 // 2-D tiled load (c0 innermost, multiple of 8 elements for 16-bit data).

@@ -30,6 +30,9 @@ cases = [  # seq, kv_len, nq, nkv, mask_type, window, gate
     (130, 1000, 4, 2, 3, oracle.INT_MAX, False),
     (257, 257, 2, 1, 0, oracle.INT_MAX, False),
     (2048, 2048, 4, 2, 3, 1024, False),
+    (600, 600, 3, 3, 3, 200, False),     # one query head per KV head: a CTA takes 256 tokens of one head
+    (520, 700, 6, 2, 3, oracle.INT_MAX, True),  # three per KV head: the same
+    (384, 384, 8, 2, 0, oracle.INT_MAX, False),  # four per KV head: two heads of a group per CTA
 ]
 for i, (seq, kv, nq, nkv, mt, w, gate) in enumerate(cases):
     q, k, v = seeded_bf16(seq, nq, 128, seed=900 + i), seeded_bf16(kv, nkv, 128, seed=950 + i), seeded_bf16(kv, nkv, 128, seed=990 + i)
