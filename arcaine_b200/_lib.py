@@ -25,6 +25,7 @@ ARC_ERR_DEVICE_WAIT_TIMEOUT = 7
 ARC_ERR_NULL_POINTER = 8
 ARC_ERR_UNSUPPORTED_GQA = 9
 ARC_ERR_TOO_LARGE = 10
+ARC_ERR_DEVICE_BAD_RANGE = 11
 
 MASK_NONE = 0
 MASK_EXPLICIT = 1
@@ -64,6 +65,7 @@ class DecodeParams(C.Structure):
         ("scale", C.c_float), ("num_ctas", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("xchg_peers", C.c_void_p), ("xchg_world", C.c_int32), ("xchg_rank", C.c_int32), ("xchg_step", C.c_uint32),
+        ("xchg_wait_cycles", C.c_int64),
     ]
 
 

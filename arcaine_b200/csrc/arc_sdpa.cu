@@ -28,9 +28,11 @@ constexpr int kMaxDevices = 64;
 // The decode kernel keeps a few bytes of static shared memory; the dynamic part
 // may use the opt-in maximum minus this reserve.
 constexpr int kDecodeStaticSmem = 1024;
+// Dynamic shared memory the decode merge kernel may ask for (it is opted in to this much).
+constexpr int kMergeSmemOptin = 64 * 1024;
 
 struct DeviceState {
-    bool ready = false;
+    std::atomic<bool> ready{false};  // set (release) once everything below is written
     uint32_t* fault = nullptr;
     int sm_count = 0;
     int smem_optin = 0;
@@ -72,9 +74,9 @@ static int device_state(DeviceState** out) {
     ARC_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return ARC_ERR_CUDA;
     DeviceState& s = g_dev[dev];
-    if (!s.ready) {
+    if (!s.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lock(g_mu);
-        if (!s.ready) {
+        if (!s.ready.load(std::memory_order_relaxed)) {
             void* sym = nullptr;
             ARC_CUDA(cudaGetSymbolAddress(&sym, g_fault_words));
             s.fault = static_cast<uint32_t*>(sym);
@@ -102,7 +104,9 @@ static int device_state(DeviceState** out) {
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 2>, s.smem_optin - kDecodeStaticSmem));
-            s.ready = true;
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<128>, kMergeSmemOptin));
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<256>, kMergeSmemOptin));
+            s.ready.store(true, std::memory_order_release);
         }
     }
     *out = &s;
@@ -305,6 +309,7 @@ struct DecodePlan {
     int smem_bytes = 0;
     long long parts = 0;
     size_t ws_bytes = 0;
+    size_t merge_smem = 0;
 };
 
 static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_optin, DecodePlan* plan) {
@@ -314,7 +319,15 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
     if (p->hd != 128 && p->hd != 256) return ARC_ERR_UNSUPPORTED_HEAD_DIM;
     if (!(p->scale > 0.f) || !std::isfinite(p->scale)) return ARC_ERR_BAD_SHAPE;
     if (!p->kv_len && p->kv_len_uniform < 0) return ARC_ERR_BAD_SHAPE;
-    if (p->kv_rows_total <= 0 || p->kv_rows_total > 0x7fffffffLL) return ARC_ERR_BAD_SHAPE;
+    if (p->kv_rows_total < 0 || p->kv_rows_total > 0x7fffffffLL) return ARC_ERR_BAD_SHAPE;
+    // An empty cache (a sequence-sharded rank whose slice holds no keys) is fine as long as the
+    // host-side length says so too.
+    if (p->kv_rows_total == 0 && (p->kv_len || p->kv_len_uniform != 0)) return ARC_ERR_BAD_SHAPE;
+    if (p->max_kv_len < 0) return ARC_ERR_BAD_SHAPE;
+    if (p->max_kv_len > 0 && !p->kv_len && p->kv_len_uniform > p->max_kv_len) return ARC_ERR_BAD_SHAPE;
+    if (!p->kv_len && !p->kv_row_offset && p->kv_len_uniform > 0 &&
+        (int64_t)(p->batch - 1) * p->kv_stride_b + p->kv_len_uniform > p->kv_rows_total)
+        return ARC_ERR_BAD_SHAPE;  // everything is known on the host: refuse at once
     const int G = p->nq / p->nkv;
     if (G > 16) return ARC_ERR_UNSUPPORTED_GQA;
     plan->nt = G > 8 ? 2 : 1;
@@ -343,6 +356,11 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
     plan->ncta = ncta;
     plan->parts = ((long long)ncta + p->batch) * slices;
     plan->ws_bytes = (size_t)plan->parts * p->nq * ((size_t)p->hd + 1) * sizeof(float);
+    // the merge kernel keeps the length prefix, a row of partial sums per warp and one weight per
+    // record of a sequence (at most ncta + 1 shares) in shared memory
+    plan->merge_smem = (size_t)(p->batch + 2) * 8 + 8 * sizeof(float) + (size_t)(MERGE_THREADS / 32) * p->hd * sizeof(float) +
+                       (size_t)(ncta + 1) * slices * sizeof(float);
+    if (plan->merge_smem > (size_t)kMergeSmemOptin) return ARC_ERR_TOO_LARGE;
     return ARC_OK;
 }
 
@@ -351,8 +369,11 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
                          cudaStream_t stream) {
     CUtensorMap tk, tv;
     int rc;
-    if ((rc = make_cache_map(&tk, p->k, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
-    if ((rc = make_cache_map(&tv, p->v, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
+    const bool empty_cache = p->kv_rows_total == 0;  // nothing to read: only the merge runs (all records empty)
+    if (!empty_cache) {
+        if ((rc = make_cache_map(&tk, p->k, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
+        if ((rc = make_cache_map(&tv, p->v, p->nkv * HD, p->kv_rows_total, p->kv_stride_t, 16 * plan.slices)) != ARC_OK) return rc;
+    }
     DecodeParams kp{};
     kp.q = static_cast<const uint16_t*>(p->q);
     kp.kv_len = p->kv_len;
@@ -372,15 +393,19 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     kp.slices = plan.slices;
     kp.stages = plan.stages;
     kp.ncta = plan.ncta;
+    kp.max_kv_len = p->max_kv_len;
+    kp.kv_rows_total = p->kv_rows_total;
 
     dim3 grid((unsigned)plan.ncta, (unsigned)plan.groups, 1);
     const unsigned threads = 32u * (unsigned)(plan.nkv_cta * plan.slices + 1);
-    if (plan.nt == 1)
-        sdpa_decode_kernel<HD, 1><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
-    else
-        sdpa_decode_kernel<HD, 2><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    ARC_CUDA(cudaGetLastError());
+    if (!empty_cache) {
+        if (plan.nt == 1)
+            sdpa_decode_kernel<HD, 1><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
+        else
+            sdpa_decode_kernel<HD, 2><<<grid, threads, plan.smem_bytes, stream>>>(tk, tv, kp);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        ARC_CUDA(cudaGetLastError());
+    }
 
     DecodeMergeParams mp{};
     mp.part_o = kp.part_o;
@@ -400,11 +425,10 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     mp.x_world = p->xchg_world;
     mp.x_rank = p->xchg_rank;
     mp.x_step = p->xchg_step;
+    mp.x_wait_cycles = p->xchg_wait_cycles > 0 ? p->xchg_wait_cycles : 2000000000LL;
     mp.fault = ds->fault;
     dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
-    const size_t merge_smem = (size_t)(p->batch + 2) * 8 + 8 * sizeof(float) + (size_t)(MERGE_THREADS / 32) * HD * sizeof(float) +
-                              (size_t)(plan.ncta + 1) * plan.slices * sizeof(float);  // a sequence spans at most ncta shares
-    sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, merge_smem, stream>>>(mp);
+    sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     ARC_CUDA(cudaGetLastError());
     return ARC_OK;
@@ -430,6 +454,7 @@ extern "C" const char* arc_sdpa_status_string(int status) {
         case ARC_ERR_NULL_POINTER: return "required pointer is null";
         case ARC_ERR_UNSUPPORTED_GQA: return "more than 16 query heads per KV head";
         case ARC_ERR_TOO_LARGE: return "size beyond a fixed limit";
+        case ARC_ERR_DEVICE_BAD_RANGE: return "a device-side kv_len or kv_row_offset reaches past the cache";
         default: return "unknown status";
     }
 }
@@ -485,14 +510,14 @@ extern "C" size_t arc_sdpa_exchange_bytes(int32_t world, int32_t batch, int32_t 
 
 extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
     if (!p) return ARC_ERR_NULL_POINTER;
-    if (!p->q || !p->k || !p->v) return ARC_ERR_NULL_POINTER;
+    if (!p->q || ((!p->k || !p->v) && p->kv_rows_total != 0)) return ARC_ERR_NULL_POINTER;
     if (!p->out && !p->out_f32) return ARC_ERR_NULL_POINTER;
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc != ARC_OK) return rc;
     DecodePlan plan;
     if ((rc = plan_decode(p, ds->sm_count, ds->smem_optin, &plan)) != ARC_OK) return rc;
-    if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || (p->out && !aligned16(p->out)) ||
+    if (!aligned16(p->q) || (p->kv_rows_total != 0 && (!aligned16(p->k) || !aligned16(p->v))) || (p->out && !aligned16(p->out)) ||
         (p->gate && !aligned16(p->gate)) || (p->out_f32 && !aligned16(p->out_f32)))
         return ARC_ERR_ALIGNMENT;
     if ((p->q_stride_b & 7) || (p->o_stride_b & 7) || (p->kv_stride_t & 7) || p->kv_stride_t < (int64_t)p->nkv * p->hd ||
@@ -525,21 +550,22 @@ extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
 // kernels receive.
 // ---------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_static_scratch[ARC_STATIC_SCRATCH_BYTES];
-static void* g_static_scratch_addr[arc::kMaxDevices];
+static std::atomic<void*> g_static_scratch_addr[arc::kMaxDevices];
 
 static int static_scratch_address(void** out) {
     int dev = 0;
     ARC_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= arc::kMaxDevices) return ARC_ERR_CUDA;
-    if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         std::lock_guard<std::mutex> lock(arc::g_mu);
-        if (g_static_scratch_addr[dev] == nullptr) {
-            void* ptr = nullptr;
+        ptr = g_static_scratch_addr[dev].load(std::memory_order_relaxed);
+        if (ptr == nullptr) {
             ARC_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
-            g_static_scratch_addr[dev] = ptr;
+            g_static_scratch_addr[dev].store(ptr, std::memory_order_release);
         }
     }
-    *out = g_static_scratch_addr[dev];
+    *out = ptr;
     return ARC_OK;
 }
 
@@ -619,6 +645,11 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     if (p->v_dst && !p->v_src && !p->k_src) return ARC_ERR_NULL_POINTER;
     if (!p->q && !p->k_src && !p->v_dst) return ARC_OK;
     if (p->seq == 0) return ARC_OK;
+    // Shared K/V projection (v_src NULL): V comes from the raw K rows, so K must not be rewritten
+    // in place — another warp may already have normalised and rotated the row V is read from.
+    if (p->v_dst && !p->v_src && p->k_dst == p->k_src) return ARC_ERR_BAD_SHAPE;
+    const int row_count = (p->q ? p->nq : 0) + (p->k_src ? p->nkv : 0) + (p->v_dst ? p->nkv : 0);
+    if (row_count == 0) return ARC_OK;  // pointers given, but no heads
     auto aligned = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
     if (!aligned(p->q) || !aligned(p->k_src) || !aligned(p->v_src) || !aligned(p->k_dst) || !aligned(p->v_dst) ||
         !aligned(p->q_weight) || !aligned(p->k_weight))
@@ -626,7 +657,12 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     const int64_t strides[] = {p->q_stride_b, p->q_stride_t, p->k_src_stride_b, p->k_src_stride_t, p->v_src_stride_b,
                                p->v_src_stride_t, p->k_dst_stride_b, p->k_dst_stride_t, p->v_dst_stride_b, p->v_dst_stride_t};
     for (int64_t st : strides)
-        if (st % 8 != 0) return ARC_ERR_ALIGNMENT;
+        if (st < 0 || st % 8 != 0) return ARC_ERR_ALIGNMENT;
+    // a token's heads must fit between two tokens
+    const int64_t qrow = (int64_t)p->nq * p->hd, kvrow = (int64_t)p->nkv * p->hd;
+    if ((p->q && p->q_stride_t < qrow) || (p->k_src && (p->k_src_stride_t < kvrow || p->k_dst_stride_t < kvrow)) ||
+        (p->v_src && p->v_src_stride_t < kvrow) || (p->v_dst && p->v_dst_stride_t < kvrow))
+        return ARC_ERR_BAD_SHAPE;
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc != ARC_OK) return rc;
@@ -675,7 +711,7 @@ extern "C" int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream) {
     // (each takes 512 / hd rows per pass), within the shared-memory angle table of 1024 pairs.
     const long long tokens = (long long)p->batch * p->seq;
     if (tokens > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
-    const int rows = (p->q ? p->nq : 0) + (p->k_src ? p->nkv : 0) + (p->v_dst ? p->nkv : 0);
+    const int rows = row_count;
     const int rows_per_pass = 8 * (512 / p->hd);
     int tpc = (8 * rows_per_pass + rows - 1) / rows;  // about eight passes per warp and round
     const int max_tpc = 1024 / (p->hd / 2);
@@ -739,7 +775,8 @@ extern "C" int arc_sdpa_device_status(uint32_t* fault_code, uint32_t* fault_deta
     if (cudaMemcpy(w, ds->fault, sizeof(w), cudaMemcpyDeviceToHost) != cudaSuccess) return ARC_ERR_CUDA;
     if (fault_code) *fault_code = w[0];
     if (fault_detail) *fault_detail = w[1];
-    return w[0] == 0 ? ARC_OK : ARC_ERR_DEVICE_WAIT_TIMEOUT;
+    if (w[0] == 0) return ARC_OK;
+    return w[0] == FAULT_BAD_KV_RANGE ? ARC_ERR_DEVICE_BAD_RANGE : ARC_ERR_DEVICE_WAIT_TIMEOUT;
 }
 
 extern "C" int arc_sdpa_clear_device_status(void) {

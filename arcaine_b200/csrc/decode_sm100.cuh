@@ -51,6 +51,8 @@ struct DecodeParams {
     int slices;   // 16-key slices per stage; consumer warps = nkv_cta * slices
     int stages;
     int ncta;     // grid.x
+    int max_kv_len;            // > 0: no sequence may be longer
+    long long kv_rows_total;   // rows addressable from k and v
 };
 
 // Prefix sums of the per-sequence lengths into shared memory: cum[b] = keys
@@ -108,6 +110,19 @@ __global__ void __launch_bounds__(288, 1)
     __shared__ uint32_t abort_flag;
     if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile uint32_t*>(p.fault);
     build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
+    if (abort_flag != 0u) return;
+    // Lengths and row offsets live on the device, so this is where they can be checked: a sequence
+    // that reaches past the cache (the copies would read zero rows and fold them in as score-0
+    // keys) or past the stated bound stops the launch with a status instead of a wrong result.
+    for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
+        const long long len = cum[b + 1] - cum[b];
+        const long long row0 = p.kv_row_offset ? p.kv_row_offset[b] : (long long)b * p.kv_stride_b;
+        if ((len > 0 && (row0 < 0 || row0 + len > p.kv_rows_total)) || (p.max_kv_len > 0 && len > p.max_kv_len)) {
+            report_fault(p.fault, FAULT_BAD_KV_RANGE, (uint32_t)b);
+            abort_flag = 1u;
+        }
+    }
+    __syncthreads();
     if (abort_flag != 0u) return;
     const long long total = cum[p.batch];
     const long long per = share_size(total, p.ncta, tk);
@@ -364,6 +379,7 @@ struct DecodeMergeParams {
     const unsigned long long* x_peers;
     int x_world, x_rank;
     uint32_t x_step;
+    long long x_wait_cycles;  // bound of the wait for the other ranks' records
     uint32_t* fault;
 };
 
@@ -419,6 +435,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
     float* acc_sm = red + 8;                                        // (warps) x HD
     float* wgt = acc_sm + (MERGE_THREADS / 32) * HD;                // one weight per record
     build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
+    if (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) return;  // block-uniform: a status is set, no work
     const int h = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total = cum[p.batch];
@@ -530,7 +547,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
             const uint32_t* f = r_flag + ((size_t)par * p.x_world + threadIdx.x) * rows + row;
             const long long t0 = clock64();
             while ((int)(ld_acquire_sys(f) - p.x_step) < 0) {
-                if (clock64() - t0 > 2000000000LL) {  // about a second: the peer never came
+                if (clock64() - t0 > p.x_wait_cycles) {  // the peer never came
                     report_fault(p.fault, FAULT_WAIT_PEER, (uint32_t)threadIdx.x);
                     x_timeout = 1;
                     break;

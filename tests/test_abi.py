@@ -77,3 +77,37 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libarc_sdpa.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_qkv_prepare_argument_validation_needs_no_gpu():
+    """Statuses that are decided before any CUDA call: an in-place K with V taken from it, parts with no
+    heads, negative or too small token strides."""
+    from arcaine_b200 import _lib
+    lib = _lib.load()
+    buf = (ctypes.c_uint16 * 4096)()
+    base = ctypes.addressof(buf)
+    base += (-base) % 16
+
+    def params(**kw):
+        p = _lib.QkvPrepareParams()
+        p.batch, p.seq, p.nq, p.nkv, p.hd = 1, 2, 2, 1, 128
+        p.q_stride_t, p.q_stride_b = 256, 512
+        for name in ("k_src", "v_src", "k_dst", "v_dst"):
+            setattr(p, name + "_stride_t", 128)
+            setattr(p, name + "_stride_b", 256)
+        p.eps, p.theta = 1e-6, 10000.0
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p
+
+    # V from the raw K projection while K is rewritten in place
+    p = params(k_src=base, k_dst=base, v_dst=base + 2048)
+    assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_ERR_BAD_SHAPE
+    # pointers given but no heads at all: nothing to do, and no division by zero
+    p = params(q=base, nq=0, nkv=0)
+    assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_OK
+    # a negative stride, and a token stride smaller than the token's heads
+    p = params(q=base, q_stride_t=-256)
+    assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_ERR_ALIGNMENT
+    p = params(q=base, q_stride_t=128)
+    assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_ERR_BAD_SHAPE

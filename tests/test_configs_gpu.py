@@ -29,7 +29,7 @@ def test_config3_sliding_window_prefill_full_size(ops):
     q, k, v = dev_randn(B, S, nq, hd, seed=3), dev_randn(B, S, nkv, hd, seed=4), dev_randn(B, S, nkv, hd, seed=5)
     out = ops.sdpa_prefill(q, k, v, scale=hd ** -0.5, mask_type=ops.MASK_CAUSAL, window=W)
     torch.cuda.synchronize()
-    for b in (0, 3):
+    for b in range(B):
         rows = sample_rows(S, nq, 600, seed=30 + b)
         want, _ = oracle.sdpa_f32(q[b].cpu(), k[b].cpu(), v[b].cpu(), scale=hd ** -0.5, mask_type=3, window=W, rows=rows)
         assert_close(out[b].reshape(-1, hd)[rows], want, f"sequence {b}")
@@ -63,7 +63,8 @@ def test_config4_gated_decode_full_size(ops):
     plain, o32, lse = ops.sdpa_decode(q, k, v, scale=hd ** -0.5, kv_len=lens.cuda(), kv_row_offset=offs.cuda(),
                                       return_partial=True)
     torch.cuda.synchronize()
-    for b in (0, 17, 40, 63):
+    shortest, longest = int(torch.argmin(lens)), int(torch.argmax(lens))
+    for b in sorted({0, 9, 17, 26, 40, 55, 63, shortest, longest}):
         o0, n = int(offs[b]), int(lens[b])
         _, want, wl = oracle.sdpa_f32(q[b:b + 1].cpu(), k[o0:o0 + n].cpu(), v[o0:o0 + n].cpu(), scale=hd ** -0.5,
                                       gate=gate[b:b + 1].cpu(), want_lse=True)
@@ -84,9 +85,9 @@ def test_config5_long_context_decode_full_size(ops):
     scale = hd ** -0.5
     out = ops.sdpa_decode(q, k, v, scale=scale)
     torch.cuda.synchronize()
-    rows = [0, 7, 8, 15]  # heads of both KV groups of one sequence
-    want, _ = oracle.sdpa_f32(q[2:3].cpu(), k[2].cpu(), v[2].cpu(), scale=scale, rows=rows)
-    assert_close(out[2][rows], want, "sequence 2")
+    for b in range(B):  # every sequence, all sixteen heads (both KV groups)
+        want, _ = oracle.sdpa_f32(q[b:b + 1].cpu(), k[b].cpu(), v[b].cpu(), scale=scale)
+        assert_close(out[b], want[0], f"sequence {b}")
     world = 8
     n = sharded.record_numel(B, nq, hd)
     gathered = torch.zeros(world, n, device="cuda")

@@ -176,3 +176,59 @@ def test_error_statuses(ops):
     ws = torch.zeros(64, dtype=torch.uint8, device="cuda")
     p.workspace, p.workspace_bytes = ws.data_ptr(), 64
     assert L.arc_sdpa_decode(C.byref(p), None) == _lib.ARC_ERR_WORKSPACE_TOO_SMALL
+
+
+def test_peer_wait_gives_up_with_a_status_and_the_device_stays_usable(ops):
+    """Sequence-sharded decode on one GPU with a second "rank" whose records never come: the merge
+    kernel's wait for them is bounded, expires (a few ms here), records FAULT_WAIT_PEER with the
+    missing source rank and returns; while the status is set launches do nothing; after a clear the
+    same call without the exchange is correct.  Nothing faults or hangs: the flag is simply never set."""
+    B, nq, nkv, hd, n = 1, 4, 1, 128, 300
+    q, k, v = seeded_bf16(B, nq, hd, seed=71), seeded_bf16(B, n, nkv, hd, seed=72), seeded_bf16(B, n, nkv, hd, seed=73)
+    xbuf = torch.zeros(ops.exchange_bytes(2, B, nq, hd), dtype=torch.uint8, device="cuda")
+    peers = torch.tensor([xbuf.data_ptr(), xbuf.data_ptr()], dtype=torch.int64, device="cuda")
+    out = torch.full((B, nq, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, out=out, exchange=(peers, 2, 0, 1),
+                    exchange_wait_cycles=20_000_000)
+    assert ops.device_status() == (ops.FAULT_WAIT_PEER, 1)   # source rank 1 never raised its flag
+    assert (out.float() == 7.0).all()                         # the merged result was never written
+    # sticky: a launch made while the status is set returns at once without touching its output
+    ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, out=out)
+    torch.cuda.synchronize()
+    assert (out.float() == 7.0).all()
+    ops.clear_device_status()
+    assert ops.device_status() == (0, 0)
+    got = ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, out=out)
+    wf, _, _ = oracle_decode(q[0], k[0], v[0], hd ** -0.5)
+    assert_close(got[0], wf[0], "decode after the status was cleared")
+
+
+def test_device_side_length_past_the_cache_is_a_status_not_a_wrong_result(ops):
+    from arcaine_b200 import _lib
+    B, nq, nkv, hd, cap = 2, 8, 2, 128, 64
+    q, k, v = seeded_bf16(B, nq, hd, seed=81), seeded_bf16(B, cap, nkv, hd, seed=82), seeded_bf16(B, cap, nkv, hd, seed=83)
+    out = torch.full((B, nq, hd), 3.0, dtype=torch.bfloat16, device="cuda")
+    bad = torch.tensor([cap, cap + 1], dtype=torch.int32, device="cuda")  # sequence 1 claims one row too many
+    ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=0.1, kv_len=bad, out=out)
+    assert ops.device_status() == (ops.FAULT_BAD_KV_RANGE, 1)
+    code, detail = C.c_uint32(0), C.c_uint32(0)
+    assert _lib.load().arc_sdpa_device_status(C.byref(code), C.byref(detail)) == _lib.ARC_ERR_DEVICE_BAD_RANGE
+    assert (out.float() == 3.0).all()
+    ops.clear_device_status()
+    # known on the host: refused before anything is launched
+    with pytest.raises(ValueError):
+        ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=0.1, kv_len=cap + 1, out=out)
+    good = torch.tensor([cap, 5], dtype=torch.int32, device="cuda")
+    got = ops.sdpa_decode(q.cuda(), k.cuda(), v.cuda(), scale=0.1, kv_len=good, out=out)
+    wf, _, _ = oracle_decode(q[1], k[1, :5], v[1, :5], 0.1)
+    assert_close(got[1], wf[0], "decode after the status was cleared")
+
+
+def test_empty_cache_slice_gives_empty_records(ops):
+    """A sequence-sharded rank whose slice holds no keys still produces its records: zeros with lse = -inf."""
+    B, nq, nkv, hd = 2, 8, 2, 128
+    q = seeded_bf16(B, nq, hd, seed=91).cuda()
+    k = torch.empty(B, 0, nkv, hd, dtype=torch.bfloat16, device="cuda")
+    out, o32, lse = ops.sdpa_decode(q, k, k, scale=0.1, return_partial=True)
+    assert torch.count_nonzero(out.float()) == 0 and torch.count_nonzero(o32) == 0
+    assert torch.isinf(lse).all() and (lse < 0).all()

@@ -158,3 +158,14 @@ def test_qwen35_form_rejects_unsupported_rotary_dim(ops):
     x = torch.zeros(4, 2, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(_lib.ArcError):
         ops.qkv_prepare(x, None, None, rotary_dim=96)   # pairs 48 apart: not a power of two
+
+
+def test_shared_kv_projection_with_in_place_k_is_refused(ops):
+    """V taken from the raw K projection while K is normalised in place would read rows another warp
+    has already rewritten: the call is refused (src/modeling/diffusion_gemma/attention.cpp:587-595 norms V
+    from a copy of raw K before k_norm runs)."""
+    B, seq, nq, nkv, hd = 1, 8, 2, 1, 128
+    q, k = seeded_bf16(B, seq, nq, hd, seed=1).cuda(), seeded_bf16(B, seq, nkv, hd, seed=2).cuda()
+    vc = torch.zeros(B, 16, nkv, hd, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError, match="k_cache"):
+        ops.qkv_prepare(q, k, None, v_from_k=True, v_cache=vc)

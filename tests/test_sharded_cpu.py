@@ -103,10 +103,7 @@ def _rank_main(rank, world, port, fail_rank):
         whole, _ = oracle.sdpa_f32(qp, k[0], v[0], scale=scale, mask_type=3)
         assert torch.allclose(torch.cat(list(parts), dim=1), whole, atol=1e-6)
         # --- a rank that fails between steps is seen by the others on the host, before the next launch
-        flag = torch.tensor([1.0 if rank == fail_rank else 0.0])
-        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-        if fail_rank >= 0:
-            assert flag.item() == 1.0
+        assert sharded.all_ranks_ok(rank != fail_rank) == (fail_rank < 0)
     finally:
         dist.destroy_process_group()
 
@@ -115,3 +112,27 @@ def _rank_main(rank, world, port, fail_rank):
 def test_world2_gloo(fail_rank):
     port = _free_port()
     mp.spawn(_rank_main, args=(2, port, fail_rank), nprocs=2, join=True)
+
+
+def test_plan_batch_shards_balances_keys():
+    """Longest-first dealing: the heaviest rank stays close to the mean where dealing by count does not."""
+    g = torch.Generator().manual_seed(4)
+    lens = torch.randint(1024, 32769, (64,), generator=g).tolist()
+    for world in (1, 2, 4, 8):
+        owned = sharded.plan_batch_shards(lens, world)
+        assert sorted(i for o in owned for i in o) == list(range(64))
+        loads = [sum(lens[i] for i in o) for o in owned]
+        assert max(loads) <= 1.03 * (sum(lens) / world)
+        assert all(o == sorted(o) for o in owned)
+    by_count = [sum(lens[i] for i in range(r * 8, r * 8 + 8)) for r in range(8)]
+    assert max(by_count) > 1.1 * (sum(lens) / 8)  # what the rule replaces
+    # more ranks than sequences: the extra ranks own nothing
+    owned = sharded.plan_batch_shards([5, 9], 4)
+    assert sorted(map(tuple, owned)) == [(), (), (0,), (1,)]
+
+
+def test_plan_seq_shards_short_sequence_leaves_empty_ranks():
+    shards = sharded.plan_seq_shards(100, 8)
+    assert shards[0] == (0, 64) and shards[1] == (64, 100)
+    assert all(s == (100, 100) for s in shards[2:])
+    assert sharded.all_ranks_ok(True) and not sharded.all_ranks_ok(False)  # no process group: local answer

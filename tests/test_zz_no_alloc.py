@@ -39,9 +39,15 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
         want = ops.sdpa_decode(q, k, v, scale=hd ** -0.5, kv_len=kl, gate=g)      # existing entry point
         got = torch.full_like(want, float("nan"))
         p = _params(q, k, v, got, g, kl)                                           # no workspace given
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = L.arc_sdpa_decode_static(C.byref(p), stream)
         assert rc == _lib.ARC_OK, L.arc_sdpa_last_error()
         torch.cuda.synchronize()
+        if call > 0:
+            # what the name promises: the call took no device memory (the first call on a device may
+            # still load the library's kernels; from the second on nothing may move)
+            assert torch.cuda.mem_get_info()[0] == free_before
         # same kernels, same schedule: identical bits; the tolerance is the suite's usual one
         assert_close(got, want.float(), f"call {call}")
         assert torch.equal(got, want)
