@@ -22,7 +22,8 @@
 // they fall into step (both wait for the tensor pipe, then both fight for the ex2 unit), so the
 // phase is enforced: the softmax warps take turns at the exponentials, block by block, through
 // a pair of mbarriers.  Per block and pipeline the issuer does
-//   wait P(j);  O += P(j) V(j);  S(j+1) = Q K(j+1)^T
+//   wait P(j);  O += P(j) V(j);  S(j+1) = Q K(j+1)^T     (P V in two halves of 64 keys, the first
+//   one as soon as its probabilities are written)
 // — P is written over S, so the next scores can only follow the P V that reads them, and both
 // come from one thread, in order.
 //
@@ -47,8 +48,8 @@ struct PairCfg {
     static constexpr int COL_S = 0;    // + 128 * pipeline
     static constexpr int COL_O = 256;  // + 128 * pipeline
     // q_full[2] q_empty[2] k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] then per pipeline:
-    // s_full p_full o_full o_empty turn fin
-    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 12;
+    // s_full p_half[2] o_full o_empty turn fin
+    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 14;
     static constexpr int FIN_FLOATS = 2 * 2 * 128 * 2;  // [tile parity][pipeline][row] (row sum, row maximum)
     static constexpr int SMEM_BYTES = (2 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + FIN_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;   // four per pipeline
@@ -164,8 +165,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
     uint64_t* v_full = k_empty + KS;
     uint64_t* v_empty = v_full + VS; // [VS] two arrivals
     uint64_t* s_full = v_empty + VS; // [2] per pipeline from here on
-    uint64_t* p_full = s_full + 2;
-    uint64_t* o_full = p_full + 2;   // one phase per tile: the tile's last O += P V has completed
+    uint64_t* p_half = s_full + 2;   // [pipeline][half]: P of keys 0-63 / 64-127 of the block is in tensor memory
+    uint64_t* o_full = p_half + 4;   // one phase per tile: the tile's last O += P V has completed
     uint64_t* o_empty = o_full + 2;  // one phase per tile: the epilogue warps have read O out
     uint64_t* turn = o_empty + 2;    // one phase per union key block: the pipeline's softmax warps are past it
     uint64_t* fin = turn + 2;        // one phase per tile: the softmax warps have published row sums and maxima
@@ -185,7 +186,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
             mbar_init(&q_full[s], 1);
             mbar_init(&q_empty[s], 1);
             mbar_init(&s_full[s], 1);
-            mbar_init(&p_full[s], 128);
+            mbar_init(&p_half[2 * s], 128);
+            mbar_init(&p_half[2 * s + 1], 128);
             mbar_init(&o_full[s], 1);
             mbar_init(&o_empty[s], 128);
             mbar_init(&turn[s], 128);
@@ -359,10 +361,10 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                             ok = false;
                             break;
                         }
-                        if (j >= pw.ulo)                        if (j < pw.ulo) {
+                        if (j < pw.ulo) {
                             // nothing to accumulate yet
                         } else if (act) {
-                            if (!mbar_wait<1>(&p_full[s], g & 1)) {
+                            if (!mbar_wait<1>(&p_half[2 * s], g & 1)) {
                                 report_fault(p.fault, FAULT_WAIT_P, g);
                                 ok = false;
                                 break;
@@ -376,11 +378,22 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                             // P from tensor memory: each 32-key chunk keeps its 16 bf16x2 columns at the
                             // start of its own 32 score columns.  V is MN-major: 64-element head-dim
                             // chunks 16 KB apart, 8-key groups 1024 bytes apart; 16 keys = 2048 bytes.
+                            // The first 64 keys go to the tensor pipe while the softmax warps are still
+                            // exponentiating the other 64.
                             const uint64_t dVs = dV + (uint64_t)((gu & 1) * (C::TILE_BYTES >> 4));
 #pragma unroll
-                            for (int kk = 0; kk < 8; ++kk)
+                            for (int kk = 0; kk < 4; ++kk)
                                 umma_ts(tO, tS + (kk >> 1) * 32 + (kk & 1) * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
                                         (j > lo || kk > 0) ? 1u : 0u);
+                            if (!mbar_wait<1>(&p_half[2 * s + 1], g & 1)) {
+                                report_fault(p.fault, FAULT_WAIT_P, 0x1000u + g);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+#pragma unroll
+                            for (int kk = 4; kk < 8; ++kk)
+                                umma_ts(tO, tS + (kk >> 1) * 32 + (kk & 1) * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV, 1u);
                             umma_commit(&v_empty[gu % VS]);
                             if (j + 1 == hi) umma_commit(&o_full[s]);
                             ++g;
@@ -627,6 +640,9 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                     tmem_st16(tS, pk);
                     if (none & 2u) zero_pk(); else chunk_exp<0>(s1, pk, ls4, sl, m_eff, kc, rm);
                     tmem_st16(tS + 32, pk);
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&p_half[2 * s]);  // keys 0-63: their share of O += P V may start
                     if (none & 4u) zero_pk(); else chunk_exp<0>(s2, pk, ls4, sl, m_eff, kc, rm);
                     tmem_st16(tS + 64, pk);
                     if (none & 8u) zero_pk(); else chunk_exp<0>(s3, pk, ls4, sl, m_eff, kc, rm);
@@ -634,7 +650,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                     l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
                     tmem_wait_st();
                     tc_fence_before_sync();
-                    mbar_arrive(&p_full[s]);
+                    mbar_arrive(&p_half[2 * s + 1]);
                     ++g;
                 }
                 mbar_arrive(&turn[s]);
