@@ -113,6 +113,25 @@ static int device_state(DeviceState** out) {
     return ARC_OK;
 }
 
+// Launch `kernel` behind the previous kernel of `stream` with programmatic serialization: its CTAs
+// may be scheduled and run up to their grid_dependency_wait() while that kernel is still running,
+// which takes the launch latency of a small follow-up kernel (a merge) off the critical path.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // (hd, heads, tokens, batch) view of a token-major bf16 tensor; box = 64 x 1 x 128 x 1, 128-byte swizzle.
@@ -294,9 +313,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         mp.nq = p->nq;
         mp.o_stride_b = p->o_stride_b;
         mp.o_stride_t = p->o_stride_t;
-        sdpa_uniform_merge_kernel<HD><<<(unsigned)plan.rows, HD / 2, 0, stream>>>(mp);
+        ARC_CUDA(launch_dependent(sdpa_uniform_merge_kernel<HD>, dim3((unsigned)plan.rows), dim3(HD / 2), 0, stream, mp));
         g_launches.fetch_add(1, std::memory_order_relaxed);
-        ARC_CUDA(cudaGetLastError());
     }
     return ARC_OK;
 }
@@ -428,9 +446,13 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     mp.x_wait_cycles = p->xchg_wait_cycles > 0 ? p->xchg_wait_cycles : 2000000000LL;
     mp.fault = ds->fault;
     dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
-    sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
+    if (empty_cache) {
+        sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
+        ARC_CUDA(cudaGetLastError());
+    } else {
+        ARC_CUDA(launch_dependent(sdpa_decode_merge_kernel<HD>, mgrid, dim3(MERGE_THREADS), plan.merge_smem, stream, mp));
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    ARC_CUDA(cudaGetLastError());
     return ARC_OK;
 }
 

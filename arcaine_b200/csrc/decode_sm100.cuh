@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(288, 1)
     const int head0 = blockIdx.y * p.nkv_cta;  // first KV head of this CTA
     const int G = p.nq / p.nkv;
 
+    grid_launch_dependents();  // the merge kernel may be scheduled now; it waits for this grid before reading
     // A fault recorded by an earlier CTA or launch: do not start new waits.
     __shared__ uint32_t abort_flag;
     if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile uint32_t*>(p.fault);
@@ -434,7 +435,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
     float* red = reinterpret_cast<float*>(cum + p.batch + 2);      // 8 floats
     float* acc_sm = red + 8;                                        // (warps) x HD
     float* wgt = acc_sm + (MERGE_THREADS / 32) * HD;                // one weight per record
-    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
+    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);  // independent of the decode kernel's results
+    grid_dependency_wait();                                        // from here on its partial records are read
     if (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) return;  // block-uniform: a status is set, no work
     const int h = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -613,6 +615,7 @@ struct UniformMergeParams {
 
 template <int HD>
 __global__ void __launch_bounds__(HD / 2) sdpa_uniform_merge_kernel(const UniformMergeParams p) {
+    grid_dependency_wait();  // launched behind the kernel that writes the partials, possibly before it has finished
     const long long row = blockIdx.x;
     const int d = threadIdx.x * 2;
     float mx = -CUDART_INF_F;

@@ -322,6 +322,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     const bool windowed = causal && p.window > 0 && p.window != 0x7fffffff;
     const int off = p.kv_len - p.seq;
 
+    grid_launch_dependents();  // with key-range splits the merge kernel follows: it may be scheduled already
     if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
     __syncthreads();
     if (*abort_slot) return;

@@ -44,6 +44,22 @@ __device__ __forceinline__ uint32_t lane_id() {
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start (be scheduled, run its prologue) while the kernel before it in the stream is still
+// running; it must call grid_dependency_wait() before touching anything that kernel writes.  The
+// earlier kernel calls grid_launch_dependents() once its CTAs no longer need the SM resources the
+// next one is waiting for to be scheduled (here: at its very start — the dependent grids are small).
+// Without the attribute both are no-ops.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
 // Register budget per warp group (four consecutive warps; every thread of the
 // group executes the same statement): a group that needs few registers hands
 // them back so that another can take more than the launch-time share.
