@@ -52,6 +52,7 @@ class PrefillParams(C.Structure):
         ("o_stride_b", C.c_int64), ("o_stride_t", C.c_int64),
         ("scale", C.c_float), ("mask_type", C.c_int32), ("window", C.c_int32), ("num_splits", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("block_ids", C.c_void_p), ("block_ids_offset", C.c_int32),
     ]
 
 

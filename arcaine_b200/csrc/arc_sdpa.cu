@@ -177,7 +177,8 @@ struct PrefillPlan {
     int q_tiles = 0;
     int splits = 1;
     long long rows = 0;
-    size_t ws_bytes = 0;
+    size_t split_bytes = 0;  // partial records of key-range splits, at the start of the workspace
+    size_t ws_bytes = 0;     // all of the workspace: partial records, then the per-row span ends of block_ids
 };
 
 static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillPlan* plan) {
@@ -206,7 +207,13 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillP
     if (splits > kv_blocks) splits = kv_blocks;
     if (splits > 64) splits = 64;
     plan->splits = splits;
-    plan->ws_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
+    plan->split_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
+    plan->split_bytes = (plan->split_bytes + 15) & ~(size_t)15;
+    plan->ws_bytes = plan->split_bytes;
+    if (p->block_ids) {
+        if (p->mask_type != ARC_MASK_CAUSAL || p->block_ids_offset < 0) return ARC_ERR_BAD_SHAPE;
+        plan->ws_bytes += ((size_t)p->seq * sizeof(int32_t) + 15) & ~(size_t)15;
+    }
     return ARC_OK;
 }
 
@@ -224,8 +231,17 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.gate = static_cast<const uint16_t*>(p->gate);
     kp.mask = p->mask_type == ARC_MASK_EXPLICIT ? p->mask : nullptr;
     kp.out_lse = p->out_lse;
-    kp.part_o = static_cast<float*>(p->workspace);
+    kp.part_o = plan.splits > 1 ? static_cast<float*>(p->workspace) : nullptr;
     kp.part_lse = kp.part_o ? kp.part_o + (size_t)plan.splits * plan.rows * HD : nullptr;
+    if (p->block_ids) {
+        // span ends per query row, once per call: a few microseconds instead of a (seq, kv_len) f32 mask
+        int* vis = reinterpret_cast<int*>(static_cast<unsigned char*>(p->workspace) + plan.split_bytes);
+        vision_span_kernel<<<(unsigned)((p->seq + 255) / 256), 256, 0, stream>>>(p->block_ids, p->block_ids_offset,
+                                                                               p->kv_len - p->seq, p->seq, p->kv_len, vis);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        ARC_CUDA(cudaGetLastError());
+        kp.vis_hi = vis;
+    }
     kp.fault = ds->fault;
     kp.batch = p->batch;
     kp.seq = p->seq;
@@ -245,7 +261,7 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
 
     // Head dim 128: two query tiles per CTA (prefill_pair_sm100.cuh) when that is the faster way to cover
     // the tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair overrides the choice (for A/B measurements).
-    if (HD == 128 && plan.splits == 1 && !(kp.mask_type == 1 && kp.mask != nullptr)) {
+    if (HD == 128 && plan.splits == 1 && !(kp.mask_type == 1 && kp.mask != nullptr) && kp.vis_hi == nullptr) {
         static const int forced = [] {
             const char* e = std::getenv("ARC_SDPA_PREFILL_KERNEL");
             if (!e) return 0;
@@ -509,7 +525,7 @@ extern "C" int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream) 
     if (p->q_stride_t < (int64_t)p->nq * p->hd || p->o_stride_t < (int64_t)p->nq * p->hd ||
         p->k_stride_t < (int64_t)p->nkv * p->hd || p->v_stride_t < (int64_t)p->nkv * p->hd)
         return ARC_ERR_BAD_SHAPE;
-    if (plan.splits > 1) {
+    if (plan.ws_bytes > 0) {
         if (!p->workspace || p->workspace_bytes < plan.ws_bytes) return ARC_ERR_WORKSPACE_TOO_SMALL;
         if (!aligned16(p->workspace)) return ARC_ERR_ALIGNMENT;
     }

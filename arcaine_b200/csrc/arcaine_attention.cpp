@@ -18,7 +18,8 @@ void throw_on(int status, const char* where) {
 // One sequence, token-major contiguous tensors: (tokens, heads, hd).
 void run_prefill(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v, bf16* out, const bf16* gate,
                  const float* mask, int seq, int kv_len, int nq, int nkv, int hd, float scale, int mask_type,
-                 int window, SdpaWorkspace& ws, const char* where) {
+                 int window, SdpaWorkspace& ws, const char* where, const int32_t* block_ids = nullptr,
+                 int block_ids_offset = 0) {
     arc_sdpa_prefill_params p{};
     p.q = q;
     p.k = k;
@@ -40,6 +41,8 @@ void run_prefill(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* 
     p.mask_type = mask_type;
     p.window = window;
     p.num_splits = 0;
+    p.block_ids = block_ids;
+    p.block_ids_offset = block_ids_offset;
     const size_t need = arc_sdpa_prefill_workspace_bytes(&p);
     if (need) {
         p.workspace = ws.reserve(need);
@@ -109,13 +112,25 @@ void gqa_attention(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, cons
 
 void batched_attention(CudaEngine& ctx, const bf16* Q_dev, int seq_len, int nq_heads, int q_head_dim,
                        const bf16* K_dev, const bf16* V_dev, int kv_len, int nkv_heads, int kv_head_dim,
-                       int /*past_offset*/, int sliding_window, float scale, bool skip_mask,
+                       int past_offset, int sliding_window, float scale, bool skip_mask,
                        const int32_t* block_ids, bf16* out, SdpaWorkspace& ws) {
-    if (block_ids) throw std::runtime_error("batched_attention: vision block ids are not supported");
     if (q_head_dim != kv_head_dim) throw std::runtime_error("batched_attention: q and kv head_dim differ");
+    if (skip_mask) block_ids = nullptr;  // the reference builds no mask at all then
+    // key j of K_dev sits at absolute position past_offset - (kv_len - seq_len) + j
+    const int ids_offset = past_offset - (kv_len - seq_len);
+    if (block_ids && ids_offset < 0) throw std::runtime_error("batched_attention: block ids start before position 0");
     run_prefill(ctx.stream, Q_dev, K_dev, V_dev, out, nullptr, nullptr, seq_len, kv_len, nq_heads, nkv_heads,
                 q_head_dim, scale, skip_mask ? ARC_MASK_NONE : ARC_MASK_CAUSAL,
-                skip_mask ? ARC_NO_WINDOW : sliding_window, ws, "batched_attention");
+                skip_mask ? ARC_NO_WINDOW : sliding_window, ws, "batched_attention", block_ids,
+                block_ids ? ids_offset : 0);
+}
+
+void gemma4_sliding_decode_attention(CudaEngine& ctx, const bf16* Q_dev, const bf16* K_cache, const bf16* V_cache,
+                                     int kv_len, int kv_start, int nq_heads, int nkv_heads, int head_dim, bf16* out,
+                                     SdpaWorkspace& ws) {
+    const size_t row = (size_t)nkv_heads * head_dim;
+    run_decode(ctx.stream, Q_dev, K_cache + (size_t)kv_start * row, V_cache + (size_t)kv_start * row, out, nullptr,
+               kv_len, nq_heads, nkv_heads, head_dim, 1.0f, ws, "gemma4_sliding_decode_attention");
 }
 
 void qwen35_xmx_attention(cudaStream_t stream, const bf16* query, const bf16* key, const bf16* value,

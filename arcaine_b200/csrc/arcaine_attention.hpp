@@ -59,11 +59,21 @@ void gqa_attention(CudaEngine& ctx, const bf16* Q, int seq, int nq, int hd, cons
                    SdpaWorkspace& ws);
 
 // src/common/layers/attention_batched.hpp:71-136.  scores*scale + causal/window
-// mask (skip_mask: no mask).  Vision block ids are not supported (throws).
+// mask (skip_mask: no mask).  block_ids (device int32 per absolute position, -1 = text): Gemma4's
+// bidirectional vision blocks (src/common/kernels/attention_mask.hpp:44-73), evaluated inside the
+// kernel; key j of K_dev sits at absolute position past_offset - (kv_len - seq_len) + j.
 void batched_attention(CudaEngine& ctx, const bf16* Q_dev, int seq_len, int nq_heads, int q_head_dim,
                        const bf16* K_dev, const bf16* V_dev, int kv_len, int nkv_heads, int kv_head_dim,
                        int past_offset, int sliding_window, float scale, bool skip_mask,
                        const int32_t* block_ids, bf16* out, SdpaWorkspace& ws);
+
+// sliding_decode_attention, src/modeling/gemma4_unified/attention.cpp:93-137: one token over cache rows
+// [kv_start, kv_start + kv_len), no scale.  Takes the token-major cache (max_seq, nkv, hd) of
+// src/modeling/gemma4_unified/kv_cache.hpp:8-9 directly: the head-major K copy and the transposed V copy the
+// reference keeps for its strided GEMMs (kv_cache.hpp:10-11) are not needed.
+void gemma4_sliding_decode_attention(CudaEngine& ctx, const bf16* Q_dev, const bf16* K_cache, const bf16* V_cache,
+                                     int kv_len, int kv_start, int nq_heads, int nkv_heads, int head_dim, bf16* out,
+                                     SdpaWorkspace& ws);
 
 // src/modeling/qwen3_5/kernels.hpp:621-679 / 761-905.  Causal GQA attention of
 // `seq` new tokens over a cache holding past + seq positions; `output` may alias

@@ -688,4 +688,21 @@ __global__ void fill_causal_mask_kernel(float* mask, const int* block_ids, int q
     }
 }
 
+// First key each query row can no longer see under the causal rule extended by Gemma4's vision
+// blocks (src/common/kernels/attention_mask.hpp:44-73): a query inside a block (same non-negative id,
+// contiguous) sees the block's later keys as well.  ids[base + j] is key j's id; row t sits at key
+// position t + off.  One thread per row; the scan runs to the end of the row's block at most.
+__global__ void vision_span_kernel(const int* ids, int base, int off, int seq, int kv_len, int* vis_hi) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= seq) return;
+    const int self = t + off;  // key index of the query's own position
+    int hi = min(max(self + 1, 0), kv_len);
+    if (self >= 0 && self < kv_len) {
+        const int id = ids[base + self];
+        if (id >= 0)
+            while (hi < kv_len && ids[base + hi] == id) ++hi;
+    }
+    vis_hi[t] = hi;
+}
+
 }  // namespace arc

@@ -37,6 +37,7 @@ struct PrefillParams {
     float* out_lse;
     float* part_o;
     float* part_lse;
+    const int* vis_hi;  // optional [seq]: first key row t can no longer see (causal rule extended by vision blocks)
     uint32_t* fault;
     int batch, seq, kv_len, nq, nkv;
     long long o_stride_b, o_stride_t;
@@ -272,7 +273,8 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
     const int q_last = min(t.q0 + C::BM - 1, p.seq - 1);
     int blk_lo = 0, blk_hi = (p.kv_len + C::BN - 1) / C::BN;
     if (causal) {
-        const int last_key = min(p.kv_len - 1, q_last + off);
+        // the span ends are monotone in the row, so the tile's last row decides
+        const int last_key = p.vis_hi ? p.vis_hi[q_last] - 1 : min(p.kv_len - 1, q_last + off);
         blk_hi = last_key >= 0 ? last_key / C::BN + 1 : 0;
         if (windowed) blk_lo = max(0, t.q0 + off - p.window + 1) / C::BN;
     }
@@ -546,6 +548,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             if (causal) {
                 const int diag = t + off;
                 row_hi = min(max(diag + 1, 0), p.kv_len);
+                if (p.vis_hi && t < p.seq) row_hi = p.vis_hi[t];  // a vision block's later keys are visible too
                 if (windowed) row_lo = max(0, diag - p.window + 1);
                 if (row_lo > row_hi) row_lo = row_hi;
             }

@@ -74,10 +74,14 @@ def sdpa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: fl
                  mask_type: int = MASK_NONE, window: int = NO_WINDOW, mask: Optional[torch.Tensor] = None,
                  gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  num_splits: int = 0, return_lse: bool = False,
-                 workspace: Optional[Workspace] = None):
+                 workspace: Optional[Workspace] = None,
+                 block_ids: Optional[torch.Tensor] = None, block_ids_offset: int = 0):
     """Prefill / canvas attention.  q: (B, S, nq, hd) or (S, nq, hd); k, v: (B, L, nkv, hd) or (L, nkv, hd).
 
     ``out`` may be ``q`` itself.  Returns ``out`` (and the natural-log LSE (B, S, nq) when asked).
+    ``block_ids`` (device int32, one per absolute position, -1 = text; causal masks only): Gemma4's
+    vision blocks — a query inside a block also sees the block's later keys
+    (src/common/kernels/attention_mask.hpp:44-73); ``block_ids[block_ids_offset + j]`` is key j's id.
     """
     squeeze = q.dim() == 3
     if squeeze:
@@ -115,6 +119,11 @@ def sdpa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: fl
     p.v_stride_b, p.v_stride_t = _token_strides(v, "v")
     p.o_stride_b, p.o_stride_t = _token_strides(out, "out")
     p.scale, p.mask_type, p.window, p.num_splits = float(scale), int(mask_type), int(window), int(num_splits)
+    if block_ids is not None:
+        _require(block_ids, torch.int32, "block_ids")
+        if not block_ids.is_contiguous() or block_ids.numel() < block_ids_offset + L or block_ids_offset < 0:
+            raise ValueError("block_ids must be contiguous and hold block_ids_offset + kv_len entries")
+        p.block_ids, p.block_ids_offset = block_ids.data_ptr(), int(block_ids_offset)
     L_ = _lib.load()
     with torch.cuda.device(q.device):
         need = L_.arc_sdpa_prefill_workspace_bytes(C.byref(p))
@@ -351,15 +360,59 @@ def gqa_attention(Q, seq, nq, hd, Kc, Vc, kv_len, nkv, past_offset, sliding_wind
 
 def batched_attention(Q, seq_len, nq_heads, q_head_dim, K, V, kv_len, nkv_heads, kv_head_dim, past_offset,
                       sliding_window, scale=1.0, skip_mask=False, block_ids=None, out=None):
-    """src/common/layers/attention_batched.hpp:71-136."""
-    del past_offset
-    if block_ids is not None:
-        raise RuntimeError("batched_attention: vision block ids are not supported")
+    """src/common/layers/attention_batched.hpp:71-136.  ``block_ids`` (device int32 per absolute position)
+    turns on the vision-block rule of fill_causal_mask_with_block_ids, evaluated inside the kernel: key j
+    of ``K`` sits at absolute position past_offset - (kv_len - seq_len) + j."""
     if q_head_dim != kv_head_dim:
         raise RuntimeError("batched_attention: q and kv head_dim differ")
+    if block_ids is not None and skip_mask:
+        block_ids = None  # the reference builds no mask at all in that case
     return sdpa_prefill(Q.view(seq_len, nq_heads, q_head_dim), K[:kv_len], V[:kv_len], scale=scale,
                         mask_type=MASK_NONE if skip_mask else MASK_CAUSAL,
-                        window=NO_WINDOW if skip_mask else sliding_window, out=out)
+                        window=NO_WINDOW if skip_mask else sliding_window, out=out,
+                        block_ids=block_ids, block_ids_offset=past_offset - (kv_len - seq_len) if block_ids is not None else 0)
+
+
+def gemma4_sliding_decode_attention(Q, K_cache, V_cache, kv_len, kv_start, nq_heads, nkv_heads, head_dim, out=None):
+    """Single-token decode of a Gemma4 sliding layer over cache rows [kv_start, kv_start + kv_len)
+    (sliding_decode_attention, src/modeling/gemma4_unified/attention.cpp:93-137; no scale: Q and K are
+    RMS-normed).  The reference keeps two extra copies of the cache for this call, K head-major
+    (nkv, max_seq, hd) and V transposed (nkv, hd, max_seq), because its strided GEMMs want them; here the
+    token-major cache (max_seq, nkv, hd) of src/modeling/gemma4_unified/kv_cache.hpp:8-9 is read in place —
+    the GQA group is folded into the MMA, so those copies and their upkeep disappear."""
+    q = Q.view(1, nq_heads, head_dim)
+    o = out.view(1, nq_heads, head_dim) if out is not None else None
+    k = K_cache.view(-1, nkv_heads, head_dim)[kv_start:kv_start + kv_len]
+    v = V_cache.view(-1, nkv_heads, head_dim)[kv_start:kv_start + kv_len]
+    res = sdpa_decode(q, k, v, scale=1.0, kv_len=kv_len, out=o)
+    return res.view(nq_heads, head_dim)
+
+
+def gemma4_full_decode_attention(Q, K_cache, V_cache, kv_len, nq_heads, head_dim, out=None):
+    """The nkv == 1 decode path of Gemma4's full-attention layers
+    (src/modeling/gemma4_unified/attention.cpp:274-288): every query head shares the one KV head, the cache
+    (kv_len, 1, hd) is read once for all of them.  Head dims 128 and 256 (the 512-wide global heads are
+    outside what the attention kernels cover)."""
+    q = Q.view(1, nq_heads, head_dim)
+    o = out.view(1, nq_heads, head_dim) if out is not None else None
+    nsplit = 1
+    if nq_heads > 16:
+        # more than 16 query heads on one KV head: the same cache rows serve several groups of <= 16 heads
+        for d in range(1, nq_heads + 1):
+            if nq_heads % d == 0 and nq_heads // d <= 16:
+                nsplit = d
+                break
+    k = K_cache.view(-1, 1, head_dim)[:kv_len]
+    v = V_cache.view(-1, 1, head_dim)[:kv_len]
+    if nsplit == 1:
+        return sdpa_decode(q, k, v, scale=1.0, kv_len=kv_len, out=o).view(nq_heads, head_dim)
+    # "batch" of nsplit query groups over the same rows (row offset 0 for all)
+    qb = q.view(nsplit, nq_heads // nsplit, head_dim)
+    ob = o.view(nsplit, nq_heads // nsplit, head_dim) if o is not None else None
+    offs = torch.zeros(nsplit, dtype=torch.int64, device=Q.device)
+    lens = torch.full((nsplit,), kv_len, dtype=torch.int32, device=Q.device)
+    res = sdpa_decode(qb, k, v, scale=1.0, kv_len=lens, kv_row_offset=offs, out=ob)
+    return res.view(nq_heads, head_dim)
 
 
 def qwen35_xmx_attention(query, key, value, output, seq, past, query_heads, key_heads, head_dim, scale):

@@ -72,7 +72,8 @@ const char* arc_sdpa_last_error(void);
  * `gate` (optional): out = bf16(attn) * sigmoid(gate), the fused form of
  * mul_sigmoid_inplace (src/modeling/qwen3_5_moe/kernels.hpp:80-88).
  * `num_splits` > 1 splits the key range over several CTAs per query tile and
- * needs `workspace` of arc_sdpa_prefill_workspace_bytes(); 0 picks a value.
+ * needs `workspace` of arc_sdpa_prefill_workspace_bytes(); 0 picks a value
+ * (ask the size function: a non-zero answer means a workspace is required).
  * ------------------------------------------------------------------------- */
 typedef struct arc_sdpa_prefill_params {
     const void* q;     /* (batch, seq, nq, hd) bf16 */
@@ -93,6 +94,15 @@ typedef struct arc_sdpa_prefill_params {
     int32_t num_splits;
     void* workspace;
     size_t workspace_bytes;
+    /* Gemma4's bidirectional vision blocks, evaluated inside the kernel (optional, ARC_MASK_CAUSAL only;
+     * fill_causal_mask_with_block_ids, src/common/kernels/attention_mask.hpp:44-73, without the
+     * (seq, kv_len) f32 buffer).  block_ids: device int32 per absolute position, -1 = text token, a
+     * non-negative id for each contiguous image / video block; a query inside a block also sees the
+     * block's later keys.  block_ids[block_ids_offset + j] belongs to key j, so the array must reach
+     * block_ids_offset + kv_len entries; the same ids serve every sequence of the batch.  Needs
+     * workspace (arc_sdpa_prefill_workspace_bytes()); head dim 128 then runs the one-tile kernel. */
+    const int32_t* block_ids;
+    int32_t block_ids_offset;
 } arc_sdpa_prefill_params;
 
 size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params* p);

@@ -138,8 +138,9 @@ def test_reference_named_entry_points(ops):
     assert_close(got, oracle.batched_attention(q, k, v, past_offset=past, scale=0.0625).float(), "batched_attention",
                  rel_tol=2e-2, abs_tol=1.5e-1)
     assert_close(got, oracle.sdpa_f32(q, k, v, scale=0.0625, mask_type=3)[0], "batched_attention vs fp32 oracle")
-    with pytest.raises(RuntimeError):
-        ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX, block_ids=torch.zeros(1))
+    with pytest.raises(ValueError):  # block ids must cover every key position
+        ops.batched_attention(q.cuda(), seq, nq, hd, kd, vd, past + seq, nkv, hd, past, oracle.INT_MAX,
+                              block_ids=torch.zeros(1, dtype=torch.int32, device="cuda"))
 
 
 def test_error_statuses(ops):
@@ -192,3 +193,52 @@ def test_vision_block_mask_buffer_and_attention(ops):
         assert_close(out, want[0], f"vision blocks, window {window}")
     plain = ops.fill_causal_mask_with_block_ids(None, seq, kv_len, past, 64, out=torch.empty(seq, kv_len, device="cuda"))
     assert torch.equal(plain, ops.fill_causal_mask(seq, kv_len, past, 64))
+
+
+@pytest.mark.parametrize("hd", [128, 256])
+def test_vision_block_ids_inside_the_kernel(ops, hd):
+    """Gemma4 vision blocks evaluated in the attention kernel (no (seq, kv_len) buffer): against the oracle
+    fed with the restated mask of src/common/kernels/attention_mask.hpp:44-73, with and without a window,
+    a block that straddles query tiles and one that starts in the past; and through batched_attention."""
+    import numpy as np
+    seq, kv_len, nq, nkv = 300, 420, 4, 2
+    past = kv_len - seq  # the cache holds every position from 0
+    ids = np.full(kv_len, -1, dtype=np.int32)
+    ids[100:190] = 0      # starts before the first query (position 120), ends inside the first tile
+    ids[230:340] = 1      # straddles the first and second query tile
+    ids[400:420] = 2      # runs to the end of the sequence
+    ids_d = torch.from_numpy(ids).cuda()
+    q, k, v = seeded_bf16(seq, nq, hd, seed=171), seeded_bf16(kv_len, nkv, hd, seed=172), seeded_bf16(kv_len, nkv, hd, seed=173)
+    for window in (oracle.INT_MAX, 150):
+        want_mask = oracle.fill_causal_mask_with_block_ids(ids, seq, kv_len, past, window)
+        want = oracle.sdpa_f32(q, k, v, scale=hd ** -0.5, mask_type=1, mask=want_mask)
+        out = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, mask_type=ops.MASK_CAUSAL, window=window,
+                               block_ids=ids_d)
+        assert_close(out, want[0], f"block ids in the kernel, window {window}")
+        plain = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, mask_type=ops.MASK_CAUSAL, window=window)
+        assert not torch.equal(plain, out)  # the blocks do change the result
+    # the reference-named call: K holds only the last 350 positions, so key 0 sits at absolute position 70
+    kv2 = 350
+    got = ops.batched_attention(q.cuda(), seq, nq, hd, k.cuda()[kv_len - kv2:], v.cuda()[kv_len - kv2:], kv2, nkv, hd,
+                                past, oracle.INT_MAX, scale=0.08, block_ids=ids_d)
+    want_mask = oracle.fill_causal_mask_with_block_ids(ids, seq, kv2, past, oracle.INT_MAX)
+    want = oracle.sdpa_f32(q, k[kv_len - kv2:], v[kv_len - kv2:], scale=0.08, mask_type=1, mask=want_mask)
+    assert_close(got, want[0], "batched_attention with block ids")
+
+
+def test_gemma4_decode_wrappers(ops):
+    """sliding_decode_attention (src/modeling/gemma4_unified/attention.cpp:93-137) over rows
+    [kv_start, kv_start + kv_len) of the token-major cache, and the nkv == 1 path (:274-288) with more than
+    16 query heads on the one KV head; no scale."""
+    nq, nkv, hd, max_seq, kv_start, kv_len = 16, 8, 256, 700, 123, 512
+    q = (seeded_bf16(nq, hd, seed=181).float() * 0.25).bfloat16()
+    kc, vc = (seeded_bf16(max_seq, nkv, hd, seed=182).float() * 0.25).bfloat16(), seeded_bf16(max_seq, nkv, hd, seed=183)
+    got = ops.gemma4_sliding_decode_attention(q.cuda(), kc.cuda(), vc.cuda(), kv_len, kv_start, nq, nkv, hd)
+    want, _ = oracle.sdpa_f32(q[None], kc[kv_start:kv_start + kv_len], vc[kv_start:kv_start + kv_len], scale=1.0)
+    assert_close(got, want[0], "gemma4 sliding decode")
+    nq1, hd1, n = 32, 128, 333
+    q1 = (seeded_bf16(nq1, hd1, seed=184).float() * 0.3).bfloat16()
+    k1, v1 = (seeded_bf16(n, 1, hd1, seed=185).float() * 0.3).bfloat16(), seeded_bf16(n, 1, hd1, seed=186)
+    got1 = ops.gemma4_full_decode_attention(q1.cuda(), k1.cuda(), v1.cuda(), n, nq1, hd1)
+    want1, _ = oracle.sdpa_f32(q1[None], k1, v1, scale=1.0)
+    assert_close(got1, want1[0], "gemma4 full-attention decode, one KV head")
