@@ -54,7 +54,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 def build_attention_bench(force: bool = False) -> str:
     """Compile the kbench-style C++ program that drives the library through the
     reference-shaped C++ interface (``arcaine_attention.hpp``)."""
-    src = os.path.join(CSRC, "attention_bench.cpp")
+    src = os.path.join(CSRC, "attention_bench.cu")
     if force or _stale(BENCH_BIN, [src, *sources()]):
         build_library()
         cmd = [_nvcc(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "--cudart", "shared", "-o", BENCH_BIN, src,

@@ -23,11 +23,17 @@ def test_bench_cells_match_the_scalar_reference_kernel(tmp_path):
         from arcaine_b200 import build
         build.build_attention_bench()
     prefills, depths = [128, 512], [0, 512, 1024]
-    res = subprocess.run([BIN, "-p", ",".join(map(str, prefills)), "-d", ",".join(map(str, depths)), "-w", "1", "-r", "3",
-                          "--dump", str(tmp_path)], capture_output=True, text=True, timeout=300)
+    res = subprocess.run([BIN, "qwen35-attention", "--warmup", "1", "--runs", "3", "--dump", str(tmp_path)],
+                         capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr
-    rows = re.findall(r"qwen35_attention kind=(\w+) kernel=sm100 q=(\d+) kv=(\d+) mean_ms=([\d.]+)", res.stdout)
+    rows = re.findall(r"qwen35_attention kind=(\w+) kernel=(sdpa\S*) q=(\d+) kv=(\d+) mean_ms=([\d.]+) sd_ms=[\d.]+ "
+                      r"max_abs=([\d.]+) max_rel=([\d.]+)", res.stdout)
     assert len(rows) == len(prefills) + 2 * len(depths)
+    # the row's own check: the library against the bench's scalar kernel on the device
+    assert all(float(r[5]) <= 2e-2 for r in rows), rows
+    assert len(re.findall(r"kernel=baseline", res.stdout)) == len(rows)
+    listing = subprocess.run([BIN, "--list"], capture_output=True, text=True, timeout=60).stdout
+    assert all(name in listing for name in ("qwen35-attention", "sdpa-prefill", "sdpa-decode"))
     nq, nkv, hd, scale = 24, 4, 256, 0.0625
     max_q, max_kv = max(prefills), max(max(prefills), max(depths) + 1)
     state = 42
