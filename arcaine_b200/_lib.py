@@ -37,6 +37,8 @@ EXPORTS = (
     "arc_sdpa_status_string", "arc_sdpa_last_error", "arc_sdpa_prefill_workspace_bytes", "arc_sdpa_prefill",
     "arc_sdpa_decode_workspace_bytes", "arc_sdpa_decode", "arc_sdpa_decode_static", "arc_sdpa_exchange_bytes", "arc_sdpa_merge", "arc_mul_sigmoid_inplace",
     "arc_fill_causal_mask", "arc_fill_causal_mask_with_block_ids", "arc_qkv_prepare", "arc_sdpa_device_status", "arc_sdpa_clear_device_status", "arc_sdpa_launch_count",
+    "arc_plan_head_shards", "arc_plan_seq_shards", "arc_plan_batch_shards", "arc_sdpa_exchange_init", "arc_sdpa_record_floats",
+    "arc_sdpa_allgather_merge",
 )
 
 
@@ -68,6 +70,11 @@ class DecodeParams(C.Structure):
         ("xchg_peers", C.c_void_p), ("xchg_world", C.c_int32), ("xchg_rank", C.c_int32), ("xchg_step", C.c_uint32),
         ("xchg_wait_cycles", C.c_int64),
     ]
+
+
+class HeadShard(C.Structure):
+    _fields_ = [("kv_head_begin", C.c_int32), ("kv_head_end", C.c_int32), ("q_head_begin", C.c_int32),
+                ("q_head_end", C.c_int32), ("batch_begin", C.c_int32), ("batch_end", C.c_int32)]
 
 
 class QkvPrepareParams(C.Structure):
@@ -135,6 +142,18 @@ def load() -> C.CDLL:
     L.arc_sdpa_clear_device_status.argtypes = []
     L.arc_sdpa_launch_count.restype = C.c_uint64
     L.arc_sdpa_launch_count.argtypes = []
+    L.arc_plan_head_shards.restype = C.c_int
+    L.arc_plan_head_shards.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(HeadShard)]
+    L.arc_plan_seq_shards.restype = C.c_int
+    L.arc_plan_seq_shards.argtypes = [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+    L.arc_plan_batch_shards.restype = C.c_int
+    L.arc_plan_batch_shards.argtypes = [C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
+    L.arc_sdpa_exchange_init.restype = C.c_int
+    L.arc_sdpa_exchange_init.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_uint64), vp, vp]
+    L.arc_sdpa_record_floats.restype = C.c_size_t
+    L.arc_sdpa_record_floats.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+    L.arc_sdpa_allgather_merge.restype = C.c_int
+    L.arc_sdpa_allgather_merge.argtypes = [vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp, vp, vp, vp]
     _lib = L
     return L
 

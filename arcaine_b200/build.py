@@ -44,7 +44,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     """Compile every kernel and the C ABI into ``libarc_sdpa.so``."""
     if force or _stale(LIB, sources()):
         cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB,
-               os.path.join(CSRC, "arc_sdpa.cu"), os.path.join(CSRC, "arcaine_attention.cpp")]
+               os.path.join(CSRC, "arc_sdpa.cu"), os.path.join(CSRC, "arcaine_attention.cpp"),
+               os.path.join(CSRC, "arc_multi_gpu.cpp"), "-ldl"]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         subprocess.check_call(cmd)

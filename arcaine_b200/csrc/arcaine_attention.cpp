@@ -273,4 +273,23 @@ void qwen35_norm_mrope_append(cudaStream_t stream, bf16* query, const bf16* key,
     throw_on(arc_qkv_prepare(&p, stream), "qwen35_norm_mrope_append");
 }
 
+arc_head_shard plan_head_shards(int nq, int nkv, int batch, int world, int rank) {
+    arc_head_shard sh{};
+    throw_on(arc_plan_head_shards(nq, nkv, batch, world, rank, &sh), "plan_head_shards");
+    return sh;
+}
+
+void plan_seq_shards(long long kv_len, int world, int rank, long long* begin, long long* end) {
+    int64_t b = 0, e = 0;
+    throw_on(arc_plan_seq_shards(kv_len, world, rank, 0, &b, &e), "plan_seq_shards");
+    *begin = b;
+    *end = e;
+}
+
+void allgather_merge(cudaStream_t stream, const float* record, float* gathered, int world, int batch, int nq, int hd,
+                     const bf16* gate, bf16* out, void* nccl_comm) {
+    throw_on(arc_sdpa_allgather_merge(record, gathered, world, batch, nq, hd, gate, out, nccl_comm, stream),
+             "allgather_merge");
+}
+
 }  // namespace arcaine

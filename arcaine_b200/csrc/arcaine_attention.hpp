@@ -12,6 +12,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include "../../include/arc_sdpa.h"
+
 #include <climits>
 #include <cstddef>
 #include <cstdint>
@@ -124,5 +126,18 @@ void qwen35_norm_mrope_append(cudaStream_t stream, bf16* query, const bf16* key,
                               bf16* value_cache, const int32_t* positions, int seq, int past, int query_heads,
                               int key_heads, int head_dim, int rotary_dim, float theta, const int sections[3],
                               const bf16* q_norm, const bf16* k_norm, float eps);
+
+// ---- multi-GPU (one process per GPU): thin forms of the C helpers that throw like the calls above ----
+
+// Which KV heads (with their query heads) and sequences rank `rank` of `world` computes in a prefill.
+arc_head_shard plan_head_shards(int nq, int nkv, int batch, int world, int rank);
+// Key range [begin, end) of rank `rank` in a sequence-sharded decode.
+void plan_seq_shards(long long kv_len, int world, int rank, long long* begin, long long* end);
+// Sequence-sharded decode through NCCL: `record` is this rank's packed [out f32 | lse f32] partial
+// (arc_sdpa_record_floats() floats, written by arc_sdpa_decode through out_f32 / out_lse), `gathered` room
+// for `world` of them; all-gather, merge, optional gate.  Replaces the host-staged copies between GPUs of
+// src/modeling/diffusion_gemma/model.cpp:33-46 for this path.
+void allgather_merge(cudaStream_t stream, const float* record, float* gathered, int world, int batch, int nq, int hd,
+                     const bf16* gate, bf16* out, void* nccl_comm);
 
 }  // namespace arcaine

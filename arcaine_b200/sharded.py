@@ -19,6 +19,7 @@ torch tensors and run unchanged on CPU tensors over ``gloo``.
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 from typing import Optional
 
@@ -44,8 +45,13 @@ class HeadShard:
         return self.kv_head_begin >= self.kv_head_end or self.batch_begin >= self.batch_end
 
 
+def _clib():
+    from . import _lib  # the planners live in the C library (include/arc_sdpa.h) so that C and C++ hosts share them
+    return _lib, _lib.load()
+
+
 def plan_head_shards(nq: int, nkv: int, batch: int, world: int) -> list[HeadShard]:
-    """Deal KV heads first, then sequences, to ``world`` ranks.
+    """Deal KV heads first, then sequences, to ``world`` ranks (``arc_plan_head_shards``).
 
     ``world`` is factored as head_ways x batch_ways with head_ways the largest
     divisor of ``world`` that also divides ``nkv``; batch_ways must then divide
@@ -53,36 +59,34 @@ def plan_head_shards(nq: int, nkv: int, batch: int, world: int) -> list[HeadShar
     """
     if nq % nkv != 0:
         raise ValueError("nq must be a multiple of nkv")
-    group = nq // nkv
-    head_ways = 1
-    for d in range(1, world + 1):
-        if world % d == 0 and nkv % d == 0:
-            head_ways = d
-    batch_ways = world // head_ways
-    heads_per = nkv // head_ways
+    _lib, L = _clib()
     shards = []
     for r in range(world):
-        hw, bw = r % head_ways, r // head_ways
-        b0 = min(batch, (batch * bw + batch_ways - 1) // batch_ways)
-        b1 = min(batch, (batch * (bw + 1) + batch_ways - 1) // batch_ways)
-        k0, k1 = hw * heads_per, (hw + 1) * heads_per
-        shards.append(HeadShard(k0, k1, k0 * group, k1 * group, b0, b1))
+        hs = _lib.HeadShard()
+        _lib.check(L.arc_plan_head_shards(nq, nkv, batch, world, r, C.byref(hs)), "arc_plan_head_shards")
+        shards.append(HeadShard(hs.kv_head_begin, hs.kv_head_end, hs.q_head_begin, hs.q_head_end,
+                                hs.batch_begin, hs.batch_end))
     return shards
 
 
 def plan_seq_shards(kv_len: int, world: int, align: int = 64) -> list[tuple[int, int]]:
-    """Contiguous [begin, end) key ranges, one per rank, boundaries aligned to ``align`` keys.
+    """Contiguous [begin, end) key ranges, one per rank, boundaries aligned to ``align`` keys
+    (``arc_plan_seq_shards``).
 
     A short sequence leaves the last ranks with an empty range ``(kv_len, kv_len)``; such a rank still
     takes part in the step (it sends records with lse = -inf), see :class:`SeqShardedDecode`.
     """
-    per = -(-kv_len // world)
-    per = -(-per // align) * align
-    return [(min(kv_len, r * per), min(kv_len, (r + 1) * per)) for r in range(world)]
+    _lib, L = _clib()
+    out = []
+    for r in range(world):
+        b, e = C.c_int64(0), C.c_int64(0)
+        _lib.check(L.arc_plan_seq_shards(kv_len, world, r, align, C.byref(b), C.byref(e)), "arc_plan_seq_shards")
+        out.append((int(b.value), int(e.value)))
+    return out
 
 
 def plan_batch_shards(lens, world: int) -> list[list[int]]:
-    """Deal whole sequences to ranks so that the ranks' key counts come out even.
+    """Deal whole sequences to ranks so that the ranks' key counts come out even (``arc_plan_batch_shards``).
 
     Decode time is proportional to the keys a rank reads, not to its number of sequences, so the
     sequences are taken longest first and each goes to the rank with the fewest keys so far (ties: the
@@ -93,13 +97,15 @@ def plan_batch_shards(lens, world: int) -> list[list[int]]:
     lens = [int(x) for x in lens]
     if world <= 0:
         raise ValueError("world must be positive")
-    load = [0] * world
+    _lib, L = _clib()
+    n = len(lens)
+    arr = (C.c_int32 * max(n, 1))(*lens)
+    owner = (C.c_int32 * max(n, 1))()
+    _lib.check(L.arc_plan_batch_shards(arr, n, world, owner), "arc_plan_batch_shards")
     owned: list[list[int]] = [[] for _ in range(world)]
-    for i in sorted(range(len(lens)), key=lambda i: (-lens[i], i)):
-        r = min(range(world), key=lambda r: (load[r], len(owned[r]), r))
-        owned[r].append(i)
-        load[r] += lens[i]
-    return [sorted(o) for o in owned]
+    for i in range(n):
+        owned[owner[i]].append(i)
+    return owned
 
 
 def all_ranks_ok(local_ok: bool, group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None) -> bool:
@@ -123,8 +129,8 @@ def all_ranks_ok(local_ok: bool, group: Optional[dist.ProcessGroup] = None, devi
 # ---------------------------------------------------------------------------
 def record_numel(batch: int, nq: int, hd: int) -> int:
     """Floats in one packed record, padded to a multiple of 4 so every part stays 16-byte aligned."""
-    n = batch * nq * hd + batch * nq
-    return (n + 3) // 4 * 4
+    _lib, L = _clib()
+    return int(L.arc_sdpa_record_floats(batch, nq, hd))
 
 
 def split_record(record: torch.Tensor, batch: int, nq: int, hd: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -197,13 +203,20 @@ class SeqShardedDecode:
         import torch.distributed._symmetric_memory as symm_mem
         nbytes = self._ops.exchange_bytes(self.world, self.batch, self.nq, self.hd)
         self._xbuf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        self._xbuf.zero_()
         grp = self.group if self.group is not None else dist.group.WORLD
         self._xhdl = symm_mem.rendezvous(self._xbuf, grp)
         ptrs = [int(x) for x in self._xhdl.buffer_ptrs]
         if len(ptrs) != self.world:
             raise RuntimeError("symmetric memory rendezvous returned an unexpected number of peers")
-        self._peers = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        # clear this rank's buffer and put the mapped peer addresses where the kernel reads them
+        # (arc_sdpa_exchange_init: the same call a C or C++ host makes)
+        self._peers = torch.empty(self.world, dtype=torch.int64, device=device)
+        _lib, L = _clib()
+        host_ptrs = (C.c_uint64 * self.world)(*ptrs)
+        with torch.cuda.device(device):
+            _lib.check(L.arc_sdpa_exchange_init(self._xbuf.data_ptr(), self.world, self.batch, self.nq, self.hd, host_ptrs,
+                                                self._peers.data_ptr(), torch.cuda.current_stream(device).cuda_stream),
+                       "arc_sdpa_exchange_init")
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)  # every rank's flags are zero before anyone stores to them
 

@@ -37,7 +37,7 @@ extern "C" {
 #define ARC_ERR_UNSUPPORTED_HEAD_DIM 3 /* hd not in {128, 256} (attention) / {128, 256, 512} (qkv_prepare) */
 #define ARC_ERR_WORKSPACE_TOO_SMALL 4
 #define ARC_ERR_CUDA 5                 /* a CUDA runtime / driver call failed */
-#define ARC_ERR_COLLECTIVE 6           /* reserved for the multi-GPU host layer */
+#define ARC_ERR_COLLECTIVE 6           /* NCCL missing or a collective failed (arc_sdpa_allgather_merge) */
 #define ARC_ERR_DEVICE_WAIT_TIMEOUT 7  /* a bounded device-side wait gave up */
 #define ARC_ERR_NULL_POINTER 8
 #define ARC_ERR_UNSUPPORTED_GQA 9      /* decode: more than 16 query heads per KV head */
@@ -291,6 +291,50 @@ typedef struct arc_qkv_prepare_params {
 } arc_qkv_prepare_params;
 
 int arc_qkv_prepare(const arc_qkv_prepare_params* p, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Multi-GPU helpers (one process per GPU).  No counterpart in the reference, whose two GPUs split
+ * layers and copy activations through host memory (src/modeling/diffusion_gemma/model.cpp:33-46);
+ * these give a C or C++ host the partitions and the record exchange without Python.
+ * ------------------------------------------------------------------------- */
+
+/* Prefill / canvas: KV heads first (with their nq / nkv query heads), then whole sequences, dealt to
+ * `world` ranks: world = head_ways x batch_ways with head_ways the largest divisor of world that
+ * divides nkv.  Rank `rank` owns KV heads [kv_head_begin, kv_head_end), query heads
+ * [q_head_begin, q_head_end) and sequences [batch_begin, batch_end) (possibly none). */
+typedef struct arc_head_shard {
+    int32_t kv_head_begin, kv_head_end;
+    int32_t q_head_begin, q_head_end;
+    int32_t batch_begin, batch_end;
+} arc_head_shard;
+int arc_plan_head_shards(int32_t nq, int32_t nkv, int32_t batch, int32_t world, int32_t rank, arc_head_shard* out);
+
+/* Long-context decode: contiguous key range [*begin, *end) of rank `rank`, boundaries on multiples of
+ * `align` keys (0 = 64).  Short sequences leave the last ranks an empty range (kv_len, kv_len). */
+int arc_plan_seq_shards(int64_t kv_len, int32_t world, int32_t rank, int32_t align, int64_t* begin, int64_t* end);
+
+/* Batched decode: whole sequences dealt to ranks longest first, each to the rank with the fewest keys so
+ * far, so that the ranks read about the same number of keys.  kv_len: HOST array [batch];
+ * owner: HOST array [batch], owner[b] = rank of sequence b. */
+int arc_plan_batch_shards(const int32_t* kv_len, int32_t batch, int32_t world, int32_t* owner);
+
+/* Exchange buffer of the in-kernel record exchange (arc_sdpa_decode_params.xchg_*): clears this rank's
+ * buffer (its flags must be zero before the first step; every rank must have done this, and the ranks
+ * must have met on the host, before anyone's first step) and copies the `world` peer addresses the caller
+ * mapped (peer access, IPC or symmetric memory; peers[rank] = this rank's own buffer) into the device
+ * array `peers_dev` [world] that xchg_peers points to.  Enqueued on `stream`. */
+int arc_sdpa_exchange_init(void* buffer, int32_t world, int32_t batch, int32_t nq, int32_t hd, const uint64_t* peers,
+                           uint64_t* peers_dev, void* stream);
+
+/* The collective form of the same exchange: ncclAllGather of this rank's packed record
+ * [out f32 (batch, nq, hd) | lse f32 (batch, nq) | padding to a multiple of 4 floats]
+ * (arc_sdpa_record_floats() floats, as arc_sdpa_decode writes it through out_f32 / out_lse when they point
+ * into one buffer) into `gathered` (world records), then the log-sum-exp merge with the optional gate
+ * into out_bf16 (batch, nq, hd).  `comm` is an ncclComm_t; the NCCL library already loaded in the process
+ * is used (else libnccl.so.2 is loaded).  ARC_ERR_COLLECTIVE if NCCL is missing or reports an error. */
+size_t arc_sdpa_record_floats(int32_t batch, int32_t nq, int32_t hd);
+int arc_sdpa_allgather_merge(const float* record, float* gathered, int32_t world, int32_t batch, int32_t nq, int32_t hd,
+                             const void* gate, void* out_bf16, void* comm, void* stream);
 
 /* Device-side status of the current device: ARC_OK, ARC_ERR_DEVICE_WAIT_TIMEOUT (the first bounded
  * wait that gave up since the last clear; fault_code says which kind, fault_detail where) or

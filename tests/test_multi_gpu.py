@@ -64,6 +64,42 @@ def _rank_main(rank, world, port):
                 _, want = oracle.sdpa_f32(q[b:b + 1], k[b], v[b], scale=scale, gate=gate[b:b + 1])
                 for mode, out in results.items():
                     assert_close(out[b:b + 1], want.float(), f"{mode} seq {b} vs oracle")
+        # the C-side collective wrapper with an ncclComm_t of the caller's own (as a C++ host has one): a
+        # communicator made through the NCCL library already in the process, its id broadcast by torch
+        import ctypes as C
+        from arcaine_b200 import _lib
+        nccl = C.CDLL("libnccl.so.2")
+
+        class UniqueId(C.Structure):
+            _fields_ = [("internal", C.c_byte * 128)]
+
+        uid = UniqueId()
+        if rank == 0:
+            assert nccl.ncclGetUniqueId(C.byref(uid)) == 0
+        idt = torch.frombuffer(bytearray(bytes(uid)), dtype=torch.uint8).to(dev)
+        dist.broadcast(idt, src=0)
+        C.memmove(C.byref(uid), bytes(idt.cpu().numpy().tobytes()), 128)
+        comm = C.c_void_p()
+        nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+        assert nccl.ncclCommInitRank(C.byref(comm), world, uid, rank) == 0
+        L_ = _lib.load()
+        n = L_.arc_sdpa_record_floats(B, nq, hd)
+        assert n == sharded.record_numel(B, nq, hd)
+        record = torch.zeros(n, dtype=torch.float32, device=dev)
+        gathered = torch.zeros(world * n, dtype=torch.float32, device=dev)
+        p_out, p_lse = sharded.split_record(record, B, nq, hd)
+        ops.sdpa_decode(qd, kl, vl, scale=scale, return_partial=True, want_out=False, partial_out=p_out, partial_lse=p_lse)
+        c_out = torch.empty(B, nq, hd, dtype=torch.bfloat16, device=dev)
+        rc = L_.arc_sdpa_allgather_merge(record.data_ptr(), gathered.data_ptr(), world, B, nq, hd, gd.data_ptr(),
+                                         c_out.data_ptr(), comm, torch.cuda.current_stream().cuda_stream)
+        assert rc == _lib.ARC_OK, rc
+        torch.cuda.synchronize()
+        assert_close(c_out, whole.float(), "arc_sdpa_allgather_merge vs one pass", rel_tol=4e-3, abs_tol=4e-3)
+        assert torch.equal(c_out, results["nccl"])  # the same collective and the same merge as the torch path
+        assert L_.arc_sdpa_allgather_merge(record.data_ptr(), gathered.data_ptr(), world, B, nq, hd, None,
+                                           c_out.data_ptr(), None, None) == _lib.ARC_ERR_NULL_POINTER
+        nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+        nccl.ncclCommDestroy(comm)
         # head-sharded prefill: each rank its KV heads; gathered slices equal the whole
         S = 300
         qp = seeded_bf16(S, nq, hd, seed=5)

@@ -136,3 +136,33 @@ def test_plan_seq_shards_short_sequence_leaves_empty_ranks():
     assert shards[0] == (0, 64) and shards[1] == (64, 100)
     assert all(s == (100, 100) for s in shards[2:])
     assert sharded.all_ranks_ok(True) and not sharded.all_ranks_ok(False)  # no process group: local answer
+
+
+def test_c_planners_against_a_plain_restatement():
+    """The planners are C functions of the library (a C++ host uses the same ones); here against the
+    rules written out in Python."""
+    for nq, nkv, batch, world in [(32, 16, 4, 1), (32, 16, 4, 2), (32, 16, 4, 8), (16, 8, 1, 8), (24, 4, 64, 8), (6, 3, 5, 4), (8, 8, 3, 16)]:
+        group = nq // nkv
+        head_ways = max(d for d in range(1, world + 1) if world % d == 0 and nkv % d == 0)
+        batch_ways, heads_per = world // head_ways, nkv // head_ways
+        got = sharded.plan_head_shards(nq, nkv, batch, world)
+        for r, sh in enumerate(got):
+            hw, bw = r % head_ways, r // head_ways
+            b0 = min(batch, (batch * bw + batch_ways - 1) // batch_ways)
+            b1 = min(batch, (batch * (bw + 1) + batch_ways - 1) // batch_ways)
+            assert (sh.kv_head_begin, sh.kv_head_end) == (hw * heads_per, (hw + 1) * heads_per)
+            assert (sh.q_head_begin, sh.q_head_end) == (hw * heads_per * group, (hw + 1) * heads_per * group)
+            assert (sh.batch_begin, sh.batch_end) == (b0, b1)
+        # every (kv head, sequence) pair is owned exactly once
+        owned = sorted((h, b) for sh in got for h in range(sh.kv_head_begin, sh.kv_head_end)
+                       for b in range(sh.batch_begin, sh.batch_end))
+        assert owned == sorted((h, b) for h in range(nkv) for b in range(batch))
+    for kv_len, world, align in [(524288, 8, 64), (5000, 2, 64), (100, 8, 64), (1000, 3, 16), (0, 4, 64)]:
+        per = -(-kv_len // world)
+        per = -(-per // align) * align
+        want = [(min(kv_len, r * per), min(kv_len, (r + 1) * per)) for r in range(world)]
+        assert sharded.plan_seq_shards(kv_len, world, align) == want
+    assert sharded.record_numel(4, 16, 128) == 4 * 16 * 128 + 4 * 16
+    assert sharded.record_numel(3, 5, 128) % 4 == 0
+    with pytest.raises(Exception):
+        sharded.plan_seq_shards(-1, 2)
