@@ -64,7 +64,7 @@ def load_traffic():
     """DRAM bytes per launch from committed ncu captures (profiles/ncu_traffic.json), keyed by workload."""
     try:
         with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            return json.load(f)
+            return {k: v for k, v in json.load(f).items() if not k.startswith("_")}
     except Exception:
         return {}
 
