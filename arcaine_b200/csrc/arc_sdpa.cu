@@ -36,6 +36,8 @@ struct DeviceState {
     uint32_t* fault = nullptr;
     int sm_count = 0;
     int smem_optin = 0;
+    // largest cluster size (2, 4 or 8; 0 = none) the cluster form of the prefill kernel can be launched with, per head dim
+    int max_cluster[2] = {0, 0};
 };
 
 static DeviceState g_dev[kMaxDevices];
@@ -100,6 +102,28 @@ static int device_state(DeviceState** out) {
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, false>, PrefillCfg<256>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, true>, PrefillCfg<256>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, true, true>, PrefillCfg<256>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, false, true>, PrefillCfg<128>::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, false, true>, PrefillCfg<256>::SMEM_BYTES));
+            for (int hi = 0; hi < 2; ++hi) {
+                for (int cs = 2; cs <= 8; cs *= 2) {
+                    cudaLaunchConfig_t cfg{};
+                    cfg.gridDim = dim3((unsigned)cs);
+                    cfg.blockDim = dim3(hi ? PrefillCfg<256>::THREADS : PrefillCfg<128>::THREADS);
+                    cfg.dynamicSmemBytes = hi ? PrefillCfg<256>::SMEM_BYTES : PrefillCfg<128>::SMEM_BYTES;
+                    cudaLaunchAttribute attr[1];
+                    attr[0].id = cudaLaunchAttributeClusterDimension;
+                    attr[0].val.clusterDim.x = (unsigned)cs;
+                    attr[0].val.clusterDim.y = 1;
+                    attr[0].val.clusterDim.z = 1;
+                    cfg.attrs = attr;
+                    cfg.numAttrs = 1;
+                    int n = 0;
+                    const cudaError_t e = hi ? cudaOccupancyMaxActiveClusters(&n, sdpa_prefill_kernel<256, false, false, true>, &cfg)
+                                             : cudaOccupancyMaxActiveClusters(&n, sdpa_prefill_kernel<128, false, false, true>, &cfg);
+                    if (e == cudaSuccess && n > 0) s.max_cluster[hi] = cs;
+                    else cudaGetLastError();
+                }
+            }
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 1>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
@@ -176,12 +200,13 @@ static int make_cache_map(CUtensorMap* tm, const void* base, int row_elems, int6
 struct PrefillPlan {
     int q_tiles = 0;
     int splits = 1;
+    int cluster = 0;         // > 0: the splits are the CTAs of a thread-block cluster of this size, folded in the kernel
     long long rows = 0;
     size_t split_bytes = 0;  // partial records of key-range splits, at the start of the workspace
     size_t ws_bytes = 0;     // all of the workspace: partial records, then the per-row span ends of block_ids
 };
 
-static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillPlan* plan) {
+static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, int max_cluster, PrefillPlan* plan) {
     if (!p) return ARC_ERR_NULL_POINTER;
     if (p->batch <= 0 || p->seq <= 0 || p->kv_len <= 0 || p->nq <= 0 || p->nkv <= 0 || p->nq % p->nkv != 0)
         return ARC_ERR_BAD_SHAPE;
@@ -206,6 +231,15 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, PrefillP
     }
     if (splits > kv_blocks) splits = kv_blocks;
     if (splits > 64) splits = 64;
+    // A split the library chose itself is run as a thread-block cluster where the device allows it: the
+    // CTAs of a tile fold their accumulators through distributed shared memory in the same launch, no
+    // partial records, no merge kernel, no workspace.  An explicit num_splits keeps the two-launch form.
+    if (p->num_splits == 0 && splits > 1 && max_cluster >= 2 && p->mask_type != ARC_MASK_EXPLICIT) {
+        int cs = 2;
+        while (cs * 2 <= splits && cs * 2 <= max_cluster) cs *= 2;
+        plan->cluster = cs;
+        splits = 1;
+    }
     plan->splits = splits;
     plan->split_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
     plan->split_bytes = (plan->split_bytes + 15) & ~(size_t)15;
@@ -261,7 +295,7 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
 
     // Head dim 128: two query tiles per CTA (prefill_pair_sm100.cuh) when that is the faster way to cover
     // the tiles.  ARC_SDPA_PREFILL_KERNEL=single|pair overrides the choice (for A/B measurements).
-    if (HD == 128 && plan.splits == 1 && !(kp.mask_type == 1 && kp.mask != nullptr) && kp.vis_hi == nullptr) {
+    if (HD == 128 && plan.splits == 1 && plan.cluster == 0 && !(kp.mask_type == 1 && kp.mask != nullptr) && kp.vis_hi == nullptr) {
         static const int forced = [] {
             const char* e = std::getenv("ARC_SDPA_PREFILL_KERNEL");
             if (!e) return 0;
@@ -295,10 +329,37 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         }
     }
 
-    // Persistent grid: one CTA per SM (fewer if there are fewer tiles), tiles dealt round-robin.
     kp.q_tiles = plan.q_tiles;
     kp.cur_heads = p->nq;
     kp.head_pair = 0;
+    if (plan.cluster > 0) {
+        // Few tiles: the key range of every tile is split over the CTAs of a thread-block cluster, which
+        // fold their accumulators through distributed shared memory — one launch, nothing in global memory
+        // but the result.  Clusters walk the tile list together.
+        const long long tiles = (long long)plan.q_tiles * p->nq * p->batch;
+        if (tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
+        kp.total_tiles = (int)tiles;
+        kp.num_splits = 1;
+        long long nclusters = ds->sm_count / plan.cluster;
+        if (nclusters > tiles) nclusters = tiles;
+        if (nclusters < 1) nclusters = 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(nclusters * plan.cluster));
+        cfg.blockDim = dim3(PrefillCfg<HD>::THREADS);
+        cfg.dynamicSmemBytes = PrefillCfg<HD>::SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)plan.cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        ARC_CUDA(cudaLaunchKernelEx(&cfg, sdpa_prefill_kernel<HD, false, false, true>, tq, tk, tv, kp));
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return ARC_OK;
+    }
+    // Persistent grid: one CTA per SM (fewer if there are fewer tiles), tiles dealt round-robin.
     const long long total_tiles = (long long)plan.q_tiles * p->nq * p->batch * plan.splits;
     if (total_tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
     kp.total_tiles = (int)total_tiles;
@@ -329,7 +390,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         mp.nq = p->nq;
         mp.o_stride_b = p->o_stride_b;
         mp.o_stride_t = p->o_stride_t;
-        ARC_CUDA(launch_dependent(sdpa_uniform_merge_kernel<HD>, dim3((unsigned)plan.rows), dim3(HD / 2), 0, stream, mp));
+        ARC_CUDA(launch_dependent(sdpa_uniform_merge_kernel<HD>, dim3((unsigned)((plan.rows + UMERGE_ROWS - 1) / UMERGE_ROWS)),
+                                  dim3(32 * UMERGE_ROWS), 0, stream, mp));
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
     return ARC_OK;
@@ -502,7 +564,7 @@ extern "C" size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params
     int sm = 148;
     if (device_state(&ds) == ARC_OK) sm = ds->sm_count;
     PrefillPlan plan;
-    if (plan_prefill(p, sm, &plan) != ARC_OK) return 0;
+    if (plan_prefill(p, sm, ds ? ds->max_cluster[p && p->hd == 256 ? 1 : 0] : 0, &plan) != ARC_OK) return 0;
     return plan.ws_bytes;
 }
 
@@ -514,7 +576,7 @@ extern "C" int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream) 
     int rc = device_state(&ds);
     if (rc != ARC_OK) return rc;
     PrefillPlan plan;
-    if ((rc = plan_prefill(p, ds->sm_count, &plan)) != ARC_OK) return rc;
+    if ((rc = plan_prefill(p, ds->sm_count, ds->max_cluster[p->hd == 256 ? 1 : 0], &plan)) != ARC_OK) return rc;
     if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
         (p->gate && !aligned16(p->gate)))
         return ARC_ERR_ALIGNMENT;
@@ -652,10 +714,11 @@ extern "C" int arc_sdpa_merge(const float* part_out, const float* part_lse, int3
     mp.lse_part_stride = part_lse_stride > 0 ? part_lse_stride : rows;
     if ((mp.o_part_stride & 3) != 0) return ARC_ERR_ALIGNMENT;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = (unsigned)((rows + UMERGE_ROWS - 1) / UMERGE_ROWS);
     if (hd == 128)
-        sdpa_uniform_merge_kernel<128><<<(unsigned)rows, 64, 0, st>>>(mp);
+        sdpa_uniform_merge_kernel<128><<<blocks, 32 * UMERGE_ROWS, 0, st>>>(mp);
     else
-        sdpa_uniform_merge_kernel<256><<<(unsigned)rows, 128, 0, st>>>(mp);
+        sdpa_uniform_merge_kernel<256><<<blocks, 32 * UMERGE_ROWS, 0, st>>>(mp);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? ARC_OK : ARC_ERR_CUDA;
 }

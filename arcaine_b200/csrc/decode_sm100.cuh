@@ -613,32 +613,72 @@ struct UniformMergeParams {
     long long o_stride_b, o_stride_t;
 };
 
+constexpr int UMERGE_ROWS = 8;  // rows per block of the uniform merge: one warp each
+
 template <int HD>
-__global__ void __launch_bounds__(HD / 2) sdpa_uniform_merge_kernel(const UniformMergeParams p) {
+__global__ void __launch_bounds__(32 * UMERGE_ROWS) sdpa_uniform_merge_kernel(const UniformMergeParams p) {
     grid_dependency_wait();  // launched behind the kernel that writes the partials, possibly before it has finished
-    const long long row = blockIdx.x;
-    const int d = threadIdx.x * 2;
+    const long long row = (long long)blockIdx.x * UMERGE_ROWS + (threadIdx.x >> 5);
+    if (row >= p.rows) return;
+    const int lane = threadIdx.x & 31;
+    constexpr int VPL = HD / 32;  // output values per lane: 4 or 8 consecutive ones
+    const int d = lane * VPL;
+    // One warp per row (a block per row spent its time being scheduled: thousands of 64-thread blocks).
+    // Parts are taken four at a time with all their loads in flight together.
+    constexpr int U = 4;
     float mx = -CUDART_INF_F;
-    for (int i = 0; i < p.num_parts; ++i) mx = fmaxf(mx, p.part_lse[(long long)i * p.lse_part_stride + row]);
-    float acc0 = 0.f, acc1 = 0.f, lse = -CUDART_INF_F;
+    for (int i0 = 0; i0 < p.num_parts; i0 += U) {
+        float li[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            li[u] = i0 + u < p.num_parts ? p.part_lse[(long long)(i0 + u) * p.lse_part_stride + row] : -CUDART_INF_F;
+#pragma unroll
+        for (int u = 0; u < U; ++u) mx = fmaxf(mx, li[u]);
+    }
+    float acc[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
+    float lse = -CUDART_INF_F;
     if (mx > -CUDART_INF_F) {
         float z = 0.f;
-        for (int i = 0; i < p.num_parts; ++i) {
-            const float li = p.part_lse[(long long)i * p.lse_part_stride + row];
-            if (li == -CUDART_INF_F) continue;
-            const float w = __expf(li - mx);
-            z += w;
-            const float2 ov = *reinterpret_cast<const float2*>(p.part_o + (long long)i * p.o_part_stride + row * HD + d);
-            acc0 = fmaf(w, ov.x, acc0);
-            acc1 = fmaf(w, ov.y, acc1);
+        for (int i0 = 0; i0 < p.num_parts; i0 += U) {
+            float li[U];
+            float4 ov[U][VPL / 4];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const bool in = i0 + u < p.num_parts;
+                li[u] = in ? p.part_lse[(long long)(i0 + u) * p.lse_part_stride + row] : -CUDART_INF_F;
+                const float* src = p.part_o + (long long)(i0 + u) * p.o_part_stride + row * HD + d;
+#pragma unroll
+                for (int j = 0; j < VPL / 4; ++j)
+                    ov[u][j] = (in && li[u] != -CUDART_INF_F) ? *reinterpret_cast<const float4*>(src + 4 * j)
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);  // an empty part's record may hold anything
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (li[u] == -CUDART_INF_F) continue;
+                const float w = __expf(li[u] - mx);
+                z += w;
+#pragma unroll
+                for (int j = 0; j < VPL / 4; ++j) {
+                    acc[4 * j] = fmaf(w, ov[u][j].x, acc[4 * j]);
+                    acc[4 * j + 1] = fmaf(w, ov[u][j].y, acc[4 * j + 1]);
+                    acc[4 * j + 2] = fmaf(w, ov[u][j].z, acc[4 * j + 2]);
+                    acc[4 * j + 3] = fmaf(w, ov[u][j].w, acc[4 * j + 3]);
+                }
+            }
         }
         const float inv = 1.f / z;
-        acc0 *= inv;
-        acc1 *= inv;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) acc[j] *= inv;
         lse = mx + __logf(z);
     }
-    if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(acc0, acc1);
-    if (p.out_lse && threadIdx.x == 0) p.out_lse[row] = lse;
+    if (p.out_f32) {
+#pragma unroll
+        for (int j = 0; j < VPL / 4; ++j)
+            *reinterpret_cast<float4*>(p.out_f32 + row * HD + d + 4 * j) = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    }
+    if (p.out_lse && lane == 0) p.out_lse[row] = lse;
     if (p.out) {
         long long eoff = row * HD + d;
         if (p.seq > 0) {
@@ -647,12 +687,19 @@ __global__ void __launch_bounds__(HD / 2) sdpa_uniform_merge_kernel(const Unifor
             const long long bb = row / ((long long)p.nq * p.seq);
             eoff = bb * p.o_stride_b + t * p.o_stride_t + hh * HD + d;
         }
-        if (p.gate) {
-            const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff);
-            acc0 = sigmoid_gate(acc0, (uint16_t)(gw & 0xffffu));
-            acc1 = sigmoid_gate(acc1, (uint16_t)(gw >> 16));
+        uint32_t packed[VPL / 2];
+#pragma unroll
+        for (int j = 0; j < VPL / 2; ++j) {
+            float a0 = acc[2 * j], a1 = acc[2 * j + 1];
+            if (p.gate) {
+                const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate + eoff + 2 * j);
+                a0 = sigmoid_gate(a0, (uint16_t)(gw & 0xffffu));
+                a1 = sigmoid_gate(a1, (uint16_t)(gw >> 16));
+            }
+            packed[j] = pack_bf16x2(a0, a1);
         }
-        *reinterpret_cast<uint32_t*>(p.out + eoff) = pack_bf16x2(acc0, acc1);
+        if (VPL == 8) *reinterpret_cast<uint4*>(p.out + eoff) = make_uint4(packed[0], packed[1], packed[VPL / 2 - 2], packed[VPL / 2 - 1]);
+        else *reinterpret_cast<uint2*>(p.out + eoff) = make_uint2(packed[0], packed[1]);
     }
 }
 

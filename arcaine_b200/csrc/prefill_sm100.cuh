@@ -23,6 +23,7 @@
 // tile's visible band are never loaded (the band idea of gqa_attention,
 // src/modeling/diffusion_gemma/attention.cpp:721-769, per CTA).
 #pragma once
+#include <type_traits>
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -75,8 +76,8 @@ struct PrefillCfg {
     static constexpr int NSB = (HD == 128) ? 3 : 2;  // score buffers: S = Q K^T runs NSB-1 blocks ahead of the softmax
     static constexpr int COL_S = 0;                  // NSB buffers of 128 fp32 columns; P (bf16) is written over them
     static constexpr int COL_O = NSB * 128;          // HD fp32 columns
-    static constexpr int NUM_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 2;
-    static constexpr int XCH_FLOATS = 2 * 2 * 128 + 2 * 128;  // row-max exchange (2 phases) + row-sum exchange
+    static constexpr int NUM_BARS = 2 + 2 * K_STAGES + 2 * V_STAGES + 2 * NSB + 1 + 2 + 2;  // the last two: cluster merge
+    static constexpr int XCH_FLOATS = 2 * 2 * 128 + 2 * 128 + 2 * 128;  // row-max exchange (2 phases), row-sum exchange, (max, sum) per row for the cluster merge
     static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;
     static constexpr int THREADS = 32 * (SOFTMAX_WARPS + 2);
@@ -106,6 +107,13 @@ __device__ __forceinline__ float masked_score(uint32_t raw, float sl, int key, c
         if (rm.mask_row && key < rm.kv_len) x += rm.mask_row[key] * 1.4426950408889634f;
     }
     return (key >= rm.lo && key < rm.hi) ? x : -CUDART_INF_F;
+}
+
+// bf16(attention) * sigmoid(gate), the rounding order of mul_sigmoid_inplace after a bf16 attention
+// output (src/modeling/qwen3_5_moe/kernels.hpp:80-88).
+__device__ __forceinline__ float sigmoid_gate_bits(float attn, uint16_t gate_bits) {
+    const float g = bf16_bits_to_f32(gate_bits);
+    return bf16_round(attn) * (1.0f / (1.0f + __expf(-g)));
 }
 
 // Maximum of one 32-column chunk, folded into four independent running maxima.
@@ -216,6 +224,9 @@ __device__ __forceinline__ void pair_sync(int quarter) {
     asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
 }
 
+// All eight softmax warps (named barrier 5; barriers 1-4 belong to pair_sync).
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 5, 256;" ::: "memory"); }
+
 // One unit of work of the persistent kernel.
 struct TileWork {
     int q0, h, b, split, kvh;
@@ -228,21 +239,23 @@ struct TileWork {
 // instead of dividing again.
 struct TileCursor {
     int w, qt, h, z;
-    int dqt, dh, dz;
-    __device__ __forceinline__ void init(const PrefillParams& p) {
-        w = blockIdx.x;
+    int dqt, dh, dz, step;
+    __device__ __forceinline__ void init(const PrefillParams& p) { init(p, blockIdx.x, gridDim.x); }
+    // first tile and stride given explicitly (a cluster of CTAs walks the list together)
+    __device__ __forceinline__ void init(const PrefillParams& p, int first, int step_) {
+        w = first;
+        step = step_;
         qt = w % p.q_tiles;
         const int rest = w / p.q_tiles;
         h = rest % p.cur_heads;
         z = rest / p.cur_heads;
-        const int step = gridDim.x;
         dqt = step % p.q_tiles;
         const int srest = step / p.q_tiles;
         dh = srest % p.cur_heads;
         dz = srest / p.cur_heads;
     }
     __device__ __forceinline__ void advance(const PrefillParams& p) {
-        w += gridDim.x;
+        w += step;
         qt += dqt;
         int carry = qt >= p.q_tiles ? 1 : 0;
         qt -= carry * p.q_tiles;
@@ -253,17 +266,24 @@ struct TileCursor {
     }
 };
 
+// nsplit > 0: the key range is split over the CTAs of a cluster (split = the CTA's rank) and the
+// tile list holds whole tiles; else the split is part of the tile index (z = batch * num_splits + split).
 template <int HD>
-__device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const TileCursor& cur) {
+__device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const TileCursor& cur, int nsplit = 0, int split = 0) {
     using C = PrefillCfg<HD>;
     TileWork t;
     t.h = cur.h;
-    if (p.num_splits == 1) {
+    if (nsplit > 0) {
+        t.b = cur.z;
+        t.split = split;
+    } else if (p.num_splits == 1) {
         t.b = cur.z;
         t.split = 0;
+        nsplit = 1;
     } else {
         t.b = cur.z / p.num_splits;
         t.split = cur.z % p.num_splits;
+        nsplit = p.num_splits;
     }
     t.kvh = p.group_shift >= 0 ? (t.h >> p.group_shift) : t.h / p.group;
     t.q0 = cur.qt * C::BM;
@@ -279,7 +299,7 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
         if (windowed) blk_lo = max(0, t.q0 + off - p.window + 1) / C::BN;
     }
     const int nblk = max(0, blk_hi - blk_lo);
-    const int per = (nblk + p.num_splits - 1) / p.num_splits;
+    const int per = (nblk + nsplit - 1) / nsplit;
     t.my_lo = blk_lo + t.split * per;
     t.n_my = max(0, min(blk_hi, t.my_lo + per) - t.my_lo);
     return t;
@@ -287,7 +307,12 @@ __device__ __forceinline__ TileWork decode_tile(const PrefillParams& p, const Ti
 
 // ADD_MASK and GATE select code that most calls do not need (an additive mask row per query, the
 // sigmoid-gated epilogue); the common instance carries neither and stays small.
-template <int HD, bool ADD_MASK, bool GATE>
+// CLUSTER: the kernel is launched in thread-block clusters; the CTAs of a cluster share a tile and
+// split its key range, then fold their accumulators through distributed shared memory — each CTA
+// writes its unnormalised O and (max, sum) per row into its own shared memory (the K / V buffers are
+// free by then), and merges a share of the rows reading all of them.  One launch, no partial records
+// in global memory, no merge kernel.
+template <int HD, bool ADD_MASK, bool GATE, bool CLUSTER = false>
 __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     sdpa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                         const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -312,10 +337,18 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     uint64_t* pv_done = p_full + NSB;   // one phase per key block: O += P V of that block has completed
     uint64_t* o_full = pv_done + 1;     // one phase per tile: the tile's last O += P V has completed
     uint64_t* o_empty = o_full + 1;     // one phase per tile: the softmax warps have read O out
+    uint64_t* part_ready = o_empty + 1;  // cluster merge, one phase per tile: every CTA's share of the tile is in its shared memory
+    uint64_t* read_done = part_ready + 1; // cluster merge, one phase per tile: every CTA has finished reading this CTA's share
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
     float* xch_max = reinterpret_cast<float*>(tmem_slot + 4);  // [phase 2][key half 2][row 128]
     float* xch_sum = xch_max + 2 * 2 * 128;                    // [key half 2][row 128]
+    float2* cl_stat = reinterpret_cast<float2*>(xch_sum + 2 * 128);  // [row 128] (max, sum) of this CTA's key range
+    const int csize = CLUSTER ? (int)cluster_nctarank() : 1;
+    const int crank = CLUSTER ? (int)cluster_ctarank() : 0;
+    const int cfirst = CLUSTER ? (int)(blockIdx.x / csize) : (int)blockIdx.x;  // this CTA's (cluster's) first tile
+    const int cstep = CLUSTER ? (int)(gridDim.x / csize) : (int)gridDim.x;
+    auto tile_of = [&](const TileCursor& c) { return CLUSTER ? decode_tile<HD>(p, c, csize, crank) : decode_tile<HD>(p, c); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -325,11 +358,10 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     const int off = p.kv_len - p.seq;
 
     grid_launch_dependents();  // with key-range splits the merge kernel follows: it may be scheduled already
-    if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
-    __syncthreads();
-    if (*abort_slot) return;
-
+    constexpr int PRODUCER_WARP = C::SOFTMAX_WARPS;
+    constexpr int MMA_WARP = C::SOFTMAX_WARPS + 1;
     if (threadIdx.x == 0) {
+        const uint32_t fault_word = *reinterpret_cast<volatile uint32_t*>(p.fault);
         mbar_init(q_full, 1);
         mbar_init(q_empty, 1);
         for (int s = 0; s < KS; ++s) {
@@ -347,31 +379,48 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         mbar_init(pv_done, 1);
         mbar_init(o_full, 1);
         mbar_init(o_empty, 32 * C::SOFTMAX_WARPS);
+        mbar_init(part_ready, csize);  // one arrival per CTA of the cluster
+        mbar_init(read_done, csize);
         fence_mbar_init();
+        *abort_slot = fault_word != 0u ? 1u : 0u;
     }
-    constexpr int PRODUCER_WARP = C::SOFTMAX_WARPS;
-    constexpr int MMA_WARP = C::SOFTMAX_WARPS + 1;
     if (warp == PRODUCER_WARP) {
+        if (lane == 0) {
+            prefetch_tensormap(&tm_q);
+            prefetch_tensormap(&tm_k);
+            prefetch_tensormap(&tm_v);
+        }
+        __syncwarp();
         tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    if constexpr (CLUSTER) cluster_sync_all();  // every CTA's barriers exist before anyone arrives on them
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    // A call that finds a status word set does no work: every role walks an empty tile list and meets
+    // the others at the end (in a cluster nobody may leave early anyway).
+    const int total_tiles = *abort_slot ? 0 : p.total_tiles;
 
     if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            prefetch_tensormap(&tm_q);
-            prefetch_tensormap(&tm_k);
-            prefetch_tensormap(&tm_v);
             int gk = 0, gv = 0, tc = 0;  // K blocks, V blocks and non-empty tiles loaded so far
+            int tn = 0;                  // tiles seen (cluster merge: one phase of read_done each)
             bool ok = true;
             TileCursor cur;
-            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
-                const TileWork tw = decode_tile<HD>(p, cur);
+            for (cur.init(p, cfirst, cstep); ok && cur.w < total_tiles; cur.advance(p), ++tn) {
+                const TileWork tw = tile_of(cur);
                 if (tw.n_my == 0) continue;
+                if constexpr (CLUSTER) {
+                    // the K / V buffers held this CTA's share of the previous tile: wait until the whole
+                    // cluster has read it
+                    if (tn > 0 && !mbar_wait_cluster(read_done, (tn - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x400u);
+                        break;
+                    }
+                }
                 if (tc > 0 && !mbar_wait(q_empty, (tc - 1) & 1)) {
                     report_fault(p.fault, FAULT_WAIT_EMPTY, 0x300u);
                     break;
@@ -379,9 +428,9 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
 #pragma unroll
                 for (int c = 0; c < C::CH; ++c) tma_load_4d(sQ + c * C::CHUNK_BYTES, &tm_q, q_full, c * 64, tw.h, tw.q0, tw.b);
+                int uk = 0, uv = 0;
                 // K runs up to K_STAGES blocks ahead of the MMAs, V up to V_STAGES; the two rings
                 // are filled in the order the MMAs will need them.
-                int uk = 0, uv = 0;
                 while (uk < tw.n_my || uv < tw.n_my) {
                     if (uk < tw.n_my && (uk <= uv + 1 || uv >= tw.n_my)) {
                         const int st = gk % KS;
@@ -453,8 +502,8 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
             };
             bool ok = true;
             TileCursor cur;
-            for (cur.init(p); ok && cur.w < p.total_tiles; cur.advance(p)) {
-                const TileWork tw = decode_tile<HD>(p, cur);
+            for (cur.init(p, cfirst, cstep); ok && cur.w < total_tiles; cur.advance(p)) {
+                const TileWork tw = tile_of(cur);
                 if (tw.n_my == 0) continue;
                 if (!mbar_wait(q_full, tc & 1)) {
                     report_fault(p.fault, FAULT_WAIT_Q, tc);
@@ -519,14 +568,170 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
         constexpr bool has_mask = ADD_MASK;  // the additive-mask form is a kernel of its own: the common one stays small
 
         int gb = 0, tc = 0;  // key blocks and non-empty tiles processed so far
+        int tn = 0;          // tiles seen (cluster merge: one phase of part_ready / read_done each)
         bool ok = true;
         uint32_t va[32], vb[32];  // this thread's 64 scores of the current block
 
+        // Cluster merge at the end of a tile.  has_blocks: this CTA's key range of the tile is not empty
+        // (m, l_share are then its row maximum and this thread's share of the row sum).
+        //
+        // Every CTA writes its unnormalised accumulator and (max, sum) per row into its own shared memory,
+        // tells the cluster with one arrival per CTA, and folds rows [crank * 128 / CS, +128 / CS): a warp
+        // takes an eighth of them, a lane 4 consecutive columns (twice for head dim 256) of every CTA's
+        // share.  A lane's 16 (32) remote 16-byte loads are issued eight at a time before any is used — the
+        // fold is bound by the latency of distributed shared memory, not by arithmetic.
+        auto fold_rows = [&](const TileWork& tw, auto cs_tag) {
+            constexpr int CS = decltype(cs_tag)::value;
+            constexpr int WROWS = 128 / CS / C::SOFTMAX_WARPS;  // rows per warp
+            constexpr int PIECES = HD / 128;                    // 16-byte pieces of a row per lane
+            constexpr int ITEMS = WROWS * PIECES;               // (row, piece) items per lane
+            constexpr int IB = CS >= 8 ? 1 : 8 / CS;            // items per batch: eight 16-byte loads in flight
+            float* opart = reinterpret_cast<float*>(sK);
+            const int row0 = crank * (128 / CS) + warp * WROWS;
+            uint2 gv[IB];
+            auto load_gates = [&](int it0) {
+                if (!p.gate) return;
+#pragma unroll
+                for (int b = 0; b < IB; ++b) {
+                    const int i = (it0 + b) / PIECES, j = (it0 + b) % PIECES;
+                    const int tt = tw.q0 + row0 + i;
+                    const long long eoff = tw.b * p.o_stride_b + tt * p.o_stride_t + (long long)tw.h * HD;
+                    gv[b] = tt < p.seq ? *reinterpret_cast<const uint2*>(p.gate + eoff + (lane + 32 * j) * 4) : make_uint2(0u, 0u);
+                }
+            };
+            // The gate values of the first batch depend on nothing here: request them before waiting for
+            // the cluster (those of a later batch go out together with its loads).
+            load_gates(0);
+            if (!__all_sync(0xffffffffu, mbar_wait_cluster(part_ready, tn & 1))) {
+                report_fault(p.fault, FAULT_WAIT_FULL, 0x700u);
+                ok = false;
+            }
+            if (!ok) return;
+            const uint32_t st_base = smem_u32(cl_stat), op_base = smem_u32(opart);
+#pragma unroll 1
+            for (int it0 = 0; it0 < ITEMS; it0 += IB) {
+                float4 o[IB][CS];
+                float2 st[IB][CS];
+                if (it0 > 0) load_gates(it0);
+#pragma unroll
+                for (int b = 0; b < IB; ++b) {
+                    const int i = (it0 + b) / PIECES, j = (it0 + b) % PIECES;
+                    const int rr = row0 + i;
+                    const uint32_t off = (uint32_t)(rr * HD + (((lane + 32 * j) ^ (rr & 7)) << 2)) * 4u;
+#pragma unroll
+                    for (int c = 0; c < CS; ++c) {
+                        st[b][c] = ld_cluster_f32x2(map_to_cta(st_base + rr * 8, c));
+                        o[b][c] = ld_cluster_f32x4(map_to_cta(op_base + off, c));
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < IB; ++b) {
+                    const int i = (it0 + b) / PIECES, j = (it0 + b) % PIECES;
+                    const int rr = row0 + i;
+                    float mx = -CUDART_INF_F, ltot = 0.f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int c = 0; c < CS; ++c) mx = fmaxf(mx, st[b][c].x);
+#pragma unroll
+                    for (int c = 0; c < CS; ++c) {
+                        // a CTA without key blocks wrote no rows: whatever was read from it is not used
+                        const float w = st[b][c].x != -CUDART_INF_F ? fast_exp2(st[b][c].x - mx) : 0.f;
+                        ltot = fmaf(w, st[b][c].y, ltot);
+                        if (w != 0.f) {
+                            acc.x = fmaf(w, o[b][c].x, acc.x);
+                            acc.y = fmaf(w, o[b][c].y, acc.y);
+                            acc.z = fmaf(w, o[b][c].z, acc.z);
+                            acc.w = fmaf(w, o[b][c].w, acc.w);
+                        }
+                    }
+                    const float inv = ltot > 0.f ? 1.0f / ltot : 0.f;
+                    const int tt = tw.q0 + rr;
+                    if (tt >= p.seq) continue;
+                    const long long eoff = tw.b * p.o_stride_b + tt * p.o_stride_t + (long long)tw.h * HD;
+                    float o4[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+                    if (p.gate) {
+                        o4[0] = sigmoid_gate_bits(o4[0], (uint16_t)(gv[b].x & 0xffffu));
+                        o4[1] = sigmoid_gate_bits(o4[1], (uint16_t)(gv[b].x >> 16));
+                        o4[2] = sigmoid_gate_bits(o4[2], (uint16_t)(gv[b].y & 0xffffu));
+                        o4[3] = sigmoid_gate_bits(o4[3], (uint16_t)(gv[b].y >> 16));
+                    }
+                    *reinterpret_cast<uint2*>(p.out + eoff + (lane + 32 * j) * 4) =
+                        make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3]));
+                    if (j == 0 && lane == 0 && p.out_lse)
+                        p.out_lse[((long long)tw.b * p.seq + tt) * p.nq + tw.h] =
+                            ltot > 0.f ? (mx + fast_log2(ltot)) * 0.6931471805599453f : -CUDART_INF_F;
+                }
+            }
+        };
+        auto cluster_tile_end = [&](const TileWork& tw, float m, float l_share, bool has_blocks) {
+            float* opart = reinterpret_cast<float*>(sK);  // [128 rows][HD] fp32, 16-byte pieces swizzled by row & 7
+            float l = 0.f;
+            // the previous tile's share (rows and statistics) must have been read by the whole cluster before
+            // this one overwrites it
+            if (tn > 0 && !__all_sync(0xffffffffu, mbar_wait_cluster(read_done, (tn - 1) & 1))) {
+                report_fault(p.fault, FAULT_WAIT_EMPTY, 0x500u);
+                ok = false;
+            }
+            if (has_blocks) {
+                xch_sum[kh * 128 + r] = l_share;
+                pair_sync(quarter);
+                l = xch_sum[r] + xch_sum[128 + r];
+                if (ok && !mbar_wait_warp(o_full, tc & 1)) {
+                    report_fault(p.fault, FAULT_WAIT_O, tc);
+                    ok = false;
+                }
+                ++tc;
+                if (ok) {
+                    tc_fence_after_sync();
+                    // this thread's half of the row, unnormalised, into this CTA's shared memory (every MMA
+                    // that read the K / V buffers has completed: o_full follows them)
+#pragma unroll 1
+                    for (int c = 0; c < OC / 32; c += 2) {
+                        tmem_ld32(tO + c * 32, va);
+                        tmem_ld32(tO + c * 32 + 32, vb);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 64; e += 4) {
+                            const uint32_t* src = e < 32 ? va + e : vb + (e - 32);
+                            const int piece = (kh * OC + c * 32 + e) >> 2;
+                            *reinterpret_cast<float4*>(opart + r * HD + ((piece ^ (r & 7)) << 2)) =
+                                make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]),
+                                            __uint_as_float(src[3]));
+                        }
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(o_empty);  // the accumulator is out: the next tile may overwrite it
+                }
+            }
+            if (kh == 0) cl_stat[r] = make_float2(has_blocks ? m : -CUDART_INF_F, l);
+            // my CTA's share is written once all 256 softmax threads are here: one thread tells every CTA of
+            // the cluster (release at cluster scope, cumulative over what the barrier ordered before it)
+            const uint32_t pr = smem_u32(part_ready), rd = smem_u32(read_done);
+            softmax_sync();
+            if (threadIdx.x == 0) {
+                fence_acq_rel_cluster();
+                for (int c = 0; c < csize; ++c) mbar_arrive_cluster(map_to_cta(pr, c));
+            }
+            if (csize == 2) fold_rows(tw, std::integral_constant<int, 2>{});
+            else if (csize == 4) fold_rows(tw, std::integral_constant<int, 4>{});
+            else fold_rows(tw, std::integral_constant<int, 8>{});
+            // every softmax thread of this CTA is done reading the cluster's shared memory
+            softmax_sync();
+            if (threadIdx.x == 0) {
+                for (int c = 0; c < csize; ++c) mbar_arrive_cluster(map_to_cta(rd, c));
+            }
+            ++tn;
+        };
+
         TileCursor cur;
-        for (cur.init(p); cur.w < p.total_tiles; cur.advance(p)) {
-            const TileWork tw = decode_tile<HD>(p, cur);
+        for (cur.init(p, cfirst, cstep); cur.w < total_tiles; cur.advance(p)) {
+            const TileWork tw = tile_of(cur);
             const int t = tw.q0 + r;
             const long long row = ((long long)tw.b * p.seq + t) * p.nq + tw.h;
+            if (CLUSTER && tw.n_my == 0) {
+                cluster_tile_end(tw, -CUDART_INF_F, 0.f, false);  // the other CTAs of the cluster may have key blocks
+                continue;
+            }
             if (tw.n_my == 0) {
                 // Nothing visible: zero output (or an empty partial) for this tile.
                 if (t < p.seq) {
@@ -588,86 +793,159 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 return true;
             };
 
-            // Block 0: publish, meet, adopt the row maximum, fetch the scores.
-            if (ok) ok = publish_max(0);
-            pair_sync(quarter);
-            if (ok) {
-                const float* xm = xch_max + (gb & 1) * 256;
-                m = fmaxf(xm[r], xm[128 + r]);
-                tmem_ld32(tS0 + (gb % NSB) * 128, va);
-                tmem_ld32(tS0 + (gb % NSB) * 128 + 32, vb);
-                tmem_wait_ld();
-            }
-
-            for (int i = 0; i < tw.n_my; ++i) {
-                const int g = gb + i;
-                const int kc = (tw.my_lo + i) * C::BN + kh * 64;
-                const uint32_t tS = tS0 + (g % NSB) * 128;
-                const bool have_next = i + 1 < tw.n_my;
-                // The next block's scores were computed one or two blocks ago: take their maximum
-                // now, so that the exchange through shared memory is hidden behind this block's
-                // exponentials.
-                if (ok && have_next) ok = publish_max(i + 1);
+            if constexpr (NSB >= 3) {
+                // Block 0: publish, meet, adopt the row maximum, fetch the scores.
+                if (ok) ok = publish_max(0);
+                pair_sync(quarter);
                 if (ok) {
-                    // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its
-                    // own 32 score columns; row-sum share in fp32.
+                    const float* xm = xch_max + (gb & 1) * 256;
+                    m = fmaxf(xm[r], xm[128 + r]);
+                    tmem_ld32(tS0 + (gb % NSB) * 128, va);
+                    tmem_ld32(tS0 + (gb % NSB) * 128 + 32, vb);
+                    tmem_wait_ld();
+                }
+
+                for (int i = 0; i < tw.n_my; ++i) {
+                    const int g = gb + i;
+                    const int kc = (tw.my_lo + i) * C::BN + kh * 64;
+                    const uint32_t tS = tS0 + (g % NSB) * 128;
+                    const bool have_next = i + 1 < tw.n_my;
+                    // The next block's scores were computed one or two blocks ago: take their maximum
+                    // now, so that the exchange through shared memory is hidden behind this block's
+                    // exponentials.
+                    if (ok && have_next) ok = publish_max(i + 1);
+                    if (ok) {
+                        // Probabilities of block i as bf16: each 32-key chunk over the first 16 of its
+                        // own 32 score columns; row-sum share in fp32.
+                        const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
+                        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                        uint32_t pk[16];
+                        if (has_mask) {
+                            chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
+                            tmem_st16(tS, pk);
+                            chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                            tmem_st16(tS + 32, pk);
+                        } else {
+                            chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
+                            tmem_st16(tS, pk);
+                            chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                            tmem_st16(tS + 32, pk);
+                        }
+                        l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive(&p_full[g % NSB]);
+                        if (have_next) {  // lands during the barrier below
+                            tmem_ld32(tS0 + ((g + 1) % NSB) * 128, va);
+                            tmem_ld32(tS0 + ((g + 1) % NSB) * 128 + 32, vb);
+                        }
+                    }
+                    if (!have_next) break;
+                    pair_sync(quarter);
+                    if (!ok) continue;
+                    const float* xm = xch_max + ((g + 1) & 1) * 256;
+                    const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
+                    const bool need = m_new > m + 8.0f;
+                    if (__any_sync(0xffffffffu, need)) {
+                        // Rare: the row maximum grows by more than 2^8 with the next block.  Once
+                        // O += P V of block i has landed, rescale this thread's half of O in tensor
+                        // memory (the row's other thread takes the same decision from the same values).
+                        const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                        tmem_wait_ld();
+                        if (!mbar_wait_warp(pv_done, g & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_O, g);
+                            ok = false;
+                            continue;
+                        }
+                        tc_fence_after_sync();
+                        uint32_t ww[32];
+    #pragma unroll 1
+                        for (int c = 0; c < OC / 32; ++c) {
+                            tmem_ld32(tO + c * 32, ww);
+                            tmem_wait_ld();
+    #pragma unroll
+                            for (int e = 0; e < 32; ++e) ww[e] = __float_as_uint(__uint_as_float(ww[e]) * alpha);
+                            tmem_st32(tO + c * 32, ww);
+                        }
+                        tmem_wait_st();
+                        l *= alpha;
+                        m = m_new;
+                    }
+                    tmem_wait_ld();
+                }
+            } else {
+                // Two score buffers leave no room to look ahead: S(i+1) can only be computed once P(i-1) has
+                // been consumed, so waiting for it before the exponentials of block i would put the tensor
+                // pipe and the softmax in series.  Here every block is taken on its own: maximum, exchange,
+                // exponentials; meanwhile the tensor pipe runs O += P(i-1) V(i-1) and S(i+1).
+                for (int i = 0; i < tw.n_my; ++i) {
+                    const int g = gb + i;
+                    const int kc = (tw.my_lo + i) * C::BN + kh * 64;
+                    const uint32_t tS = tS0 + (g % NSB) * 128;
+                    if (ok && !mbar_wait_warp(&s_full[g % NSB], (g / NSB) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_S, g);
+                        ok = false;
+                    }
+                    if (ok) {
+                        tc_fence_after_sync();
+                        tmem_ld32(tS, va);
+                        tmem_ld32(tS + 32, vb);
+                        tmem_wait_ld();
+                        float mr[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                        float ms[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+                        chunk_max_any<has_mask>(va, mr, ms, sl, kc, rm);
+                        chunk_max_any<has_mask>(vb, mr, ms, sl, kc + 32, rm);
+                        xch_max[(g & 1) * 256 + kh * 128 + r] = fmaxf(fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * sl,
+                                                                     fmaxf(fmaxf(ms[0], ms[1]), fmaxf(ms[2], ms[3])));
+                    }
+                    pair_sync(quarter);
+                    if (!ok) continue;
+                    const float* xm = xch_max + (g & 1) * 256;
+                    const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
+                    if (i == 0) {
+                        m = m_new;  // nothing accumulated yet
+                    } else if (__any_sync(0xffffffffu, m_new > m + 8.0f)) {
+                        // Rare: the row maximum grows by more than 2^8.  Once O += P V of the previous block has
+                        // landed, rescale this thread's half of O in tensor memory (the row's other thread takes
+                        // the same decision from the same values).
+                        const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
+                        if (!mbar_wait_warp(pv_done, (g - 1) & 1)) {
+                            report_fault(p.fault, FAULT_WAIT_O, g);
+                            ok = false;
+                            continue;
+                        }
+                        tc_fence_after_sync();
+                        uint32_t ww[32];
+#pragma unroll 1
+                        for (int c = 0; c < OC / 32; ++c) {
+                            tmem_ld32(tO + c * 32, ww);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) ww[e] = __float_as_uint(__uint_as_float(ww[e]) * alpha);
+                            tmem_st32(tO + c * 32, ww);
+                        }
+                        tmem_wait_st();
+                        l *= alpha;
+                        m = m_new;
+                    }
                     const float m_eff = (m == -CUDART_INF_F) ? 0.f : m;
                     float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                     uint32_t pk[16];
-                    if (has_mask) {
-                        chunk_exp_any<true>(va, pk, ls4, sl, m_eff, kc, rm);
-                        tmem_st16(tS, pk);
-                        chunk_exp_any<true>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                        tmem_st16(tS + 32, pk);
-                    } else {
-                        chunk_exp_any<false>(va, pk, ls4, sl, m_eff, kc, rm);
-                        tmem_st16(tS, pk);
-                        chunk_exp_any<false>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
-                        tmem_st16(tS + 32, pk);
-                    }
+                    chunk_exp_any<has_mask>(va, pk, ls4, sl, m_eff, kc, rm);
+                    tmem_st16(tS, pk);
+                    chunk_exp_any<has_mask>(vb, pk, ls4, sl, m_eff, kc + 32, rm);
+                    tmem_st16(tS + 32, pk);
                     l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(&p_full[g % NSB]);
-                    if (have_next) {  // lands during the barrier below
-                        tmem_ld32(tS0 + ((g + 1) % NSB) * 128, va);
-                        tmem_ld32(tS0 + ((g + 1) % NSB) * 128 + 32, vb);
-                    }
                 }
-                if (!have_next) break;
-                pair_sync(quarter);
-                if (!ok) continue;
-                const float* xm = xch_max + ((g + 1) & 1) * 256;
-                const float m_new = fmaxf(m, fmaxf(xm[r], xm[128 + r]));
-                const bool need = m_new > m + 8.0f;
-                if (__any_sync(0xffffffffu, need)) {
-                    // Rare: the row maximum grows by more than 2^8 with the next block.  Once
-                    // O += P V of block i has landed, rescale this thread's half of O in tensor
-                    // memory (the row's other thread takes the same decision from the same values).
-                    const float alpha = (m_new == -CUDART_INF_F) ? 1.0f : fast_exp2(m - m_new);
-                    tmem_wait_ld();
-                    if (!mbar_wait_warp(pv_done, g & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_O, g);
-                        ok = false;
-                        continue;
-                    }
-                    tc_fence_after_sync();
-                    uint32_t ww[32];
-#pragma unroll 1
-                    for (int c = 0; c < OC / 32; ++c) {
-                        tmem_ld32(tO + c * 32, ww);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) ww[e] = __float_as_uint(__uint_as_float(ww[e]) * alpha);
-                        tmem_st32(tO + c * 32, ww);
-                    }
-                    tmem_wait_st();
-                    l *= alpha;
-                    m = m_new;
-                }
-                tmem_wait_ld();
             }
             gb += tw.n_my;
+            if constexpr (CLUSTER) {
+                cluster_tile_end(tw, m, l, true);
+                continue;
+            }
 
             // Row sum = the two threads' shares.
             xch_sum[kh * 128 + r] = l;
@@ -758,6 +1036,9 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     tc_fence_before_sync();
     __syncthreads();
     if (warp == PRODUCER_WARP) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    // A CTA's shared memory may be read by the others only while it is alive: nobody leaves before the
+    // whole cluster is through (all threads are still running here).
+    if constexpr (CLUSTER) cluster_sync_all();
 }
 
 }  // namespace arc

@@ -87,6 +87,21 @@ def test_key_range_splits_agree(ops, splits):
     run_case(ops, 256, 1100, 4, 2, 256, 0.0625, 3, 700, seed=31, num_splits=splits, lse=True)
 
 
+@pytest.mark.parametrize("hd", [128, 256])
+@pytest.mark.parametrize("seq,kv_len,nq,nkv,mask_type,window", [
+    (130, 2100, 4, 2, 0, oracle.INT_MAX),    # 8 tiles, 17 key blocks: clusters of 8, ragged last tile
+    (130, 2100, 4, 2, 3, 100),               # the same with a window: most CTAs of a cluster see no key
+    (256, 1200, 8, 4, 3, oracle.INT_MAX),    # 16 tiles, 10 key blocks: clusters of 4
+    (256, 700, 24, 4, 0, oracle.INT_MAX),    # 48 tiles, 6 key blocks: clusters of 2
+    (200, 517, 6, 2, 3, 300),                # ragged in both directions
+])
+def test_cluster_fold_of_key_range_splits(ops, hd, seq, kv_len, nq, nkv, mask_type, window):
+    """Splits the library chooses itself run as one thread-block cluster per tile whose CTAs fold their
+    accumulators through distributed shared memory; with the gate and the log-sum-exp output."""
+    run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=500 + hd + seq, gate=True, lse=True)
+    run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=600 + hd + seq)
+
+
 def test_gate_epilogue_and_split_gate(ops):
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True)
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True, num_splits=2)
