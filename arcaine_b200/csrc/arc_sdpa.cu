@@ -452,10 +452,10 @@ static int plan_decode(const arc_sdpa_decode_params* p, int sm_count, int smem_o
     plan->ncta = ncta;
     plan->parts = ((long long)ncta + p->batch) * slices;
     plan->ws_bytes = (size_t)plan->parts * p->nq * ((size_t)p->hd + 1) * sizeof(float);
-    // the merge kernel keeps the length prefix, a row of partial sums per warp and one weight per
-    // record of a sequence (at most ncta + 1 shares) in shared memory
+    // the merge kernel keeps the length prefix, a row of partial sums per warp and one weight plus one
+    // list entry per record of a sequence (at most ncta + 1 shares) in shared memory
     plan->merge_smem = (size_t)(p->batch + 2) * 8 + 8 * sizeof(float) + (size_t)(MERGE_THREADS / 32) * p->hd * sizeof(float) +
-                       (size_t)(ncta + 1) * slices * sizeof(float);
+                       (size_t)(ncta + 1) * slices * (sizeof(float) + sizeof(int));
     if (plan->merge_smem > (size_t)kMergeSmemOptin) return ARC_ERR_TOO_LARGE;
     return ARC_OK;
 }

@@ -80,11 +80,12 @@ void run_decode(cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v
 }  // namespace
 
 SdpaWorkspace::~SdpaWorkspace() {
-    if (ptr_) cudaFree(ptr_);
+    if (ptr_ && owned_) cudaFree(ptr_);
 }
 
 void* SdpaWorkspace::reserve(size_t bytes) {
     if (bytes > bytes_) {
+        if (!owned_) throw std::runtime_error("SdpaWorkspace: the borrowed region is too small for this call");
         if (ptr_) cudaFree(ptr_);
         ptr_ = nullptr;
         bytes_ = 0;

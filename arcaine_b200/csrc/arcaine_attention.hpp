@@ -35,6 +35,9 @@ struct CudaEngine {
 class SdpaWorkspace {
 public:
     SdpaWorkspace() = default;
+    // A region the caller owns (an arena slice sized from arc_sdpa_*_workspace_bytes): never freed or grown
+    // here; a call that needs more throws.
+    SdpaWorkspace(void* borrowed, size_t bytes) : ptr_(borrowed), bytes_(bytes), owned_(false) {}
     ~SdpaWorkspace();
     SdpaWorkspace(const SdpaWorkspace&) = delete;
     SdpaWorkspace& operator=(const SdpaWorkspace&) = delete;
@@ -44,6 +47,7 @@ public:
 private:
     void* ptr_ = nullptr;
     size_t bytes_ = 0;
+    bool owned_ = true;
 };
 
 // src/modeling/diffusion_gemma/attention.cpp:930-995.  O = softmax(Q K^T + mask) V,

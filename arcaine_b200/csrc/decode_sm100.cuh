@@ -81,6 +81,11 @@ __device__ __forceinline__ long long share_size(long long total, int ncta, int t
     return per > 0 ? per : tile_keys;
 }
 
+// All consumer warps of the CTA (named barrier 1; the producer warp does not take part).
+__device__ __forceinline__ void consumer_sync(int consumer_warps) {
+    asm volatile("bar.sync 1, %0;" ::"r"(consumer_warps * 32) : "memory");
+}
+
 template <int HD, int NT>
 __global__ void __launch_bounds__(288, 1)
     sdpa_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -194,6 +199,7 @@ __global__ void __launch_bounds__(288, 1)
 
         int it = 0;
         bool ok = true;
+        bool folded = false;  // this warp has been through the two barriers of the in-CTA fold
         int b = b_first;
         long long g = g0;
         while (ok && g < g1) {
@@ -323,6 +329,19 @@ __global__ void __launch_bounds__(288, 1)
             }
 
             // Partial record of this (CTA, sequence, slice): normalised out + natural-log lse.
+            // The last segment of the share (for most CTAs the only one) is folded across the slices inside
+            // the CTA first: the stages are free by then, so each warp leaves its record in shared memory,
+            // and the warps of a KV head combine them into ONE record per (CTA, sequence), stored in slice
+            // 0's slot; the other slices' slots are marked empty (lse = -inf).  The merge kernel then reads
+            // `slices` times fewer records.  Earlier segments (a sequence boundary inside the share) write
+            // one record per slice.
+            const bool fold_here = p.slices > 1 && seg_end == g1;  // CTA-uniform
+            float* rec = reinterpret_cast<float*>(stage_base);     // [warp][NT * 8 heads][HD]
+            float* rec_lse = rec + (size_t)ncw * NT * 8 * HD;      // [warp][NT * 8]
+            if (fold_here) {
+                consumer_sync(ncw);  // every warp is through with the stages; no copy is in flight any more
+                folded = true;
+            }
             if (ok) {
                 const long long part = ((long long)blockIdx.x + b) * p.slices + slice;
 #pragma unroll
@@ -336,15 +355,18 @@ __global__ void __launch_bounds__(288, 1)
                         ls += __shfl_xor_sync(0xffffffffu, ls, 16);
                         inv[u] = ls > 0.f ? 1.f / ls : 0.f;
                         const int n = nt * 8 + q4 * 2 + u;
-                        if (g4 == 0 && n < G)
-                            p.part_lse[part * p.nq + (long long)kvh * G + n] =
-                                ls > 0.f ? (m[nt][u] + fast_log2(ls)) * 0.6931471805599453f : -CUDART_INF_F;
+                        const float lse = ls > 0.f ? (m[nt][u] + fast_log2(ls)) * 0.6931471805599453f : -CUDART_INF_F;
+                        if (g4 == 0) {
+                            if (fold_here) rec_lse[warp * NT * 8 + n] = lse;
+                            else if (n < G) p.part_lse[part * p.nq + (long long)kvh * G + n] = lse;
+                        }
                     }
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         const int n = nt * 8 + q4 * 2 + u;
-                        if (n < G) {
-                            float* dst = p.part_o + (part * p.nq + (long long)kvh * G + n) * HD;
+                        if (fold_here || n < G) {
+                            float* dst = fold_here ? rec + ((size_t)warp * NT * 8 + n) * HD
+                                                   : p.part_o + (part * p.nq + (long long)kvh * G + n) * HD;
 #pragma unroll
                             for (int mt = 0; mt < HD / 16; ++mt) {
                                 dst[mt * 16 + g4] = o[nt][mt][u] * inv[u];
@@ -354,7 +376,45 @@ __global__ void __launch_bounds__(288, 1)
                     }
                 }
             }
+            if (fold_here) {
+                consumer_sync(ncw);  // all records of the CTA are in shared memory
+                // The `slices` warps of this KV head share its G x HD output values, four per step.
+                const long long part0 = ((long long)blockIdx.x + b) * p.slices;
+                for (int item = slice * 32 + lane; item < G * (HD / 4); item += p.slices * 32) {
+                    const int n = item / (HD / 4), d = (item % (HD / 4)) * 4;
+                    float mx = -CUDART_INF_F;
+                    for (int sidx = 0; sidx < p.slices; ++sidx)
+                        mx = fmaxf(mx, rec_lse[(sidx * p.nkv_cta + hl) * NT * 8 + n]);
+                    float z = 0.f;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (mx > -CUDART_INF_F) {
+                        for (int sidx = 0; sidx < p.slices; ++sidx) {
+                            const int w = sidx * p.nkv_cta + hl;
+                            const float li = rec_lse[w * NT * 8 + n];
+                            if (li == -CUDART_INF_F) continue;
+                            const float wt = __expf(li - mx);
+                            z += wt;
+                            const float4 ov = *reinterpret_cast<const float4*>(rec + ((size_t)w * NT * 8 + n) * HD + d);
+                            acc.x = fmaf(wt, ov.x, acc.x);
+                            acc.y = fmaf(wt, ov.y, acc.y);
+                            acc.z = fmaf(wt, ov.z, acc.z);
+                            acc.w = fmaf(wt, ov.w, acc.w);
+                        }
+                        const float iz = 1.f / z;
+                        acc = make_float4(acc.x * iz, acc.y * iz, acc.z * iz, acc.w * iz);
+                    }
+                    const long long row = part0 * p.nq + (long long)kvh * G + n;
+                    *reinterpret_cast<float4*>(p.part_o + row * HD + d) = acc;
+                    if (d == 0) p.part_lse[row] = mx > -CUDART_INF_F ? mx + __logf(z) : -CUDART_INF_F;
+                }
+                if (slice > 0 && lane < G) p.part_lse[(part0 + slice) * p.nq + (long long)kvh * G + lane] = -CUDART_INF_F;
+            }
             g = seg_end;
+        }
+        // A warp that gave up a wait never reached the fold: it still meets the others at both barriers.
+        if (p.slices > 1 && !folded) {
+            consumer_sync(ncw);
+            consumer_sync(ncw);
         }
     }
 }
@@ -435,6 +495,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
     float* red = reinterpret_cast<float*>(cum + p.batch + 2);      // 8 floats
     float* acc_sm = red + 8;                                        // (warps) x HD
     float* wgt = acc_sm + (MERGE_THREADS / 32) * HD;                // one weight per record
+    __shared__ int n_live_sm;
     build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);  // independent of the decode kernel's results
     grid_dependency_wait();                                        // from here on its partial records are read
     if (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) return;  // block-uniform: a status is set, no work
@@ -472,17 +533,36 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
         if (z > 0.f) {
             inv = 1.f / z;
             lse = mx + __logf(z);
-            // each warp folds every 8th record, four at a time so that their loads are in flight
+            // Most records carry no weight (the decode kernel folds the slices of a share's last segment
+            // into slice 0's slot and marks the others empty; slots of other sequences' shares): warp 0
+            // lists the live ones, in order, so that the fold below is spread evenly and always adds in the
+            // same order.
+            int* live = reinterpret_cast<int*>(wgt + n_parts);
+            if (warp == 0) {
+                int base = 0;
+                for (int i0 = 0; i0 < n_parts; i0 += 32) {
+                    const int i = i0 + lane;
+                    const bool on = i < n_parts && wgt[i] != 0.f;
+                    const uint32_t bal = __ballot_sync(0xffffffffu, on);
+                    if (on) live[base + __popc(bal & ((1u << lane) - 1u))] = i;
+                    base += __popc(bal);
+                }
+                if (lane == 0) n_live_sm = base;
+            }
+            __syncthreads();
+            const int n_live = n_live_sm;
+            // each warp folds every 8th live record, four at a time so that their loads are in flight
             // together (one record after the other, the loop ran at one L2 latency per record);
             // a lane owns VPL consecutive output values
             constexpr int NW = MERGE_THREADS / 32, U = 4;
-            for (int i0 = warp; i0 < n_parts; i0 += NW * U) {
+            for (int j0 = warp; j0 < n_live; j0 += NW * U) {
                 float w[U];
                 float4 ov[U][VPL / 4];
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int i = i0 + u * NW;
-                    w[u] = i < n_parts ? wgt[i] : 0.f;
+                    const int jj = j0 + u * NW;
+                    const int i = jj < n_live ? live[jj] : 0;
+                    w[u] = jj < n_live ? wgt[i] : 0.f;
                     const float* src = p.part_o + ((part0 + i) * p.nq + h) * HD + lane * VPL;
 #pragma unroll
                     for (int j = 0; j < VPL / 4; ++j)

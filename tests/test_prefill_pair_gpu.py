@@ -1,7 +1,9 @@
-"""Parity of the experimental two-tiles-per-CTA prefill kernel (head dim 128) with the CPU oracle.
+"""Parity of the two-tiles-per-CTA prefill kernel (head dim 128) with the CPU oracle.
 
-The kernel is opt-in through ARC_SDPA_PREFILL_KERNEL=pair, read once per process, so the cases run in a
-child process with that variable set.
+The library picks this kernel by a cost model (large problems); ARC_SDPA_PREFILL_KERNEL=pair, read once per
+process, forces it for every head-dim-128 call, so the small cases here run in a child process with that
+variable set: two token tiles of one head (odd GQA group), two heads of one KV group over the same tokens (even
+group), masks, windows, gate and ragged ends.
 """
 import os
 import subprocess
