@@ -626,7 +626,7 @@ extern "C" int arc_sdpa_decode(const arc_sdpa_decode_params* p, void* stream) {
     if (p->gate && !p->out) return ARC_ERR_NULL_POINTER;
     if (p->xchg_world > 1) {
         if (!p->xchg_peers || !p->out) return ARC_ERR_NULL_POINTER;
-        if (p->xchg_rank < 0 || p->xchg_rank >= p->xchg_world || p->xchg_world > MERGE_THREADS) return ARC_ERR_BAD_SHAPE;
+        if (p->xchg_rank < 0 || p->xchg_rank >= p->xchg_world || p->xchg_world > XCHG_MAX_WORLD) return ARC_ERR_BAD_SHAPE;
     }
     if (!p->workspace || p->workspace_bytes < plan.ws_bytes) return ARC_ERR_WORKSPACE_TOO_SMALL;
     if (!aligned16(p->workspace)) return ARC_ERR_ALIGNMENT;

@@ -444,24 +444,24 @@ struct DecodeMergeParams {
     uint32_t* fault;
 };
 
-// Layout of one rank's exchange buffer: two parities x world sources x rows records, stored as
-// three arrays (out f32 [2][world][rows][hd], lse f32 [2][world][rows], flag u32 [2][world][rows]).
-__host__ __device__ inline size_t xchg_lse_offset(int world, long long rows, int hd) {
-    return (size_t)2 * world * rows * hd * sizeof(float);
-}
-__host__ __device__ inline size_t xchg_flag_offset(int world, long long rows, int hd) {
-    return xchg_lse_offset(world, rows, hd) + (size_t)2 * world * rows * sizeof(float);
-}
+// Layout of one rank's exchange buffer: [2 parities][world sources][rows] records of HD + 2 words, a word
+// being 8 bytes = (value bits, step).  Every value travels with the step number it belongs to, so a
+// receiver recognises a word as soon as it lands: no fence between data and a separate flag, one NVLink
+// crossing per exchange instead of three (stores, their acknowledgement, the flag).  Words HD and HD + 1
+// hold the row's log-sum-exp and padding.  8-byte stores are single transactions; a 16-byte store may be
+// split, which is fine because each half carries its own step.
+constexpr int XCHG_MAX_WORLD = 16;  // ranks of one exchange (one NVSwitch box has 8)
+__host__ __device__ inline size_t xchg_record_words(int hd) { return (size_t)hd + 2; }
 __host__ __device__ inline size_t xchg_total_bytes(int world, long long rows, int hd) {
-    return xchg_flag_offset(world, rows, hd) + (size_t)2 * world * rows * sizeof(uint32_t);
+    return (size_t)2 * world * rows * xchg_record_words(hd) * 8;
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -599,58 +599,64 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
         if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(a0, a1);
     }
     if (p.x_world > 1) {
-        // Sequence-sharded: this rank's (out, lse) of the row goes straight into every rank's
-        // exchange buffer over NVLink (plain peer stores), followed by a release-store of the step
-        // number into that rank's flag for (source, row).  Then the block waits — for a bounded
-        // time — until all sources' flags for its row show this step, and folds the records.
+        // Sequence-sharded: this rank's (out, lse) of the row goes straight into every rank's exchange
+        // buffer over NVLink as plain peer stores of (value, step) words.  Then the block waits — for a
+        // bounded time — until the words of every source rank show this step, and folds the records.
+        // Thread t < HD / 2 sends and receives values 2t, 2t + 1 (one 16-byte store / load); thread HD / 2
+        // does the same for the log-sum-exp word and hands the sources' values round through shared memory.
         const long long rows = (long long)p.batch * p.nq;
         const int par = (int)(p.x_step & 1u);
+        const size_t rw = xchg_record_words(HD) / 2;  // 16-byte units per record
         const size_t slot = ((size_t)par * p.x_world + p.x_rank) * rows + row;
-        for (int dst = 0; dst < p.x_world; ++dst) {
-            unsigned char* base = reinterpret_cast<unsigned char*>(p.x_peers[dst]);
-            if (threadIdx.x < HD / 2)
-                *reinterpret_cast<float2*>(reinterpret_cast<float*>(base) + slot * HD + d) = make_float2(a0, a1);
-            if (threadIdx.x == 0) reinterpret_cast<float*>(base + xchg_lse_offset(p.x_world, rows, HD))[slot] = lse;
+        const bool sender = threadIdx.x <= HD / 2;
+        if (sender) {
+            const uint4 word = threadIdx.x < HD / 2 ? make_uint4(__float_as_uint(a0), p.x_step, __float_as_uint(a1), p.x_step)
+                                                    : make_uint4(__float_as_uint(lse), p.x_step, 0u, p.x_step);
+            for (int dst = 0; dst < p.x_world; ++dst)
+                st_volatile_v4(reinterpret_cast<uint4*>(p.x_peers[dst]) + slot * rw + threadIdx.x, word);
         }
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x < p.x_world) {
-            unsigned char* base = reinterpret_cast<unsigned char*>(p.x_peers[threadIdx.x]);
-            st_release_sys(reinterpret_cast<uint32_t*>(base + xchg_flag_offset(p.x_world, rows, HD)) + slot, p.x_step);
-        }
-        unsigned char* mine = reinterpret_cast<unsigned char*>(p.x_peers[p.x_rank]);
-        const float* r_out = reinterpret_cast<const float*>(mine);
-        const float* r_lse = reinterpret_cast<const float*>(mine + xchg_lse_offset(p.x_world, rows, HD));
-        const uint32_t* r_flag = reinterpret_cast<const uint32_t*>(mine + xchg_flag_offset(p.x_world, rows, HD));
+        const uint4* mine = reinterpret_cast<const uint4*>(p.x_peers[p.x_rank]);
         __shared__ int x_timeout;
+        __shared__ float x_lse[XCHG_MAX_WORLD];
         if (threadIdx.x == 0) x_timeout = 0;
         __syncthreads();
-        if (threadIdx.x < p.x_world) {
-            const uint32_t* f = r_flag + ((size_t)par * p.x_world + threadIdx.x) * rows + row;
+        float b0 = 0.f, b1 = 0.f, z = 0.f;
+        float2 rv[XCHG_MAX_WORLD];  // this thread's two values from every source
+        if (sender) {
             const long long t0 = clock64();
-            while ((int)(ld_acquire_sys(f) - p.x_step) < 0) {
-                if (clock64() - t0 > p.x_wait_cycles) {  // the peer never came
-                    report_fault(p.fault, FAULT_WAIT_PEER, (uint32_t)threadIdx.x);
-                    x_timeout = 1;
-                    break;
+            bool gave_up = false;
+#pragma unroll
+            for (int src = 0; src < XCHG_MAX_WORLD; ++src) {
+                if (src >= p.x_world) break;
+                const uint4* w = mine + (((size_t)par * p.x_world + src) * rows + row) * rw + threadIdx.x;
+                uint4 v = ld_volatile_v4(w);
+                while (!gave_up && (v.y != p.x_step || v.w != p.x_step)) {
+                    if (clock64() - t0 > p.x_wait_cycles) {  // the peer never came
+                        report_fault(p.fault, FAULT_WAIT_PEER, (uint32_t)src);
+                        x_timeout = 1;
+                        gave_up = true;
+                        break;
+                    }
+                    v = ld_volatile_v4(w);
                 }
+                rv[src] = make_float2(__uint_as_float(v.x), __uint_as_float(v.z));
+                if (threadIdx.x == HD / 2) x_lse[src] = rv[src].x;
             }
         }
-        __syncthreads();
+        __syncthreads();  // x_lse[] and x_timeout are visible
         if (x_timeout) return;
         float mx = -CUDART_INF_F;
-        for (int src = 0; src < p.x_world; ++src) mx = fmaxf(mx, r_lse[((size_t)par * p.x_world + src) * rows + row]);
-        float z = 0.f, b0 = 0.f, b1 = 0.f;
+        for (int src = 0; src < p.x_world; ++src) mx = fmaxf(mx, x_lse[src]);
         if (mx > -CUDART_INF_F && threadIdx.x < HD / 2) {
-            for (int src = 0; src < p.x_world; ++src) {
-                const size_t sl = ((size_t)par * p.x_world + src) * rows + row;
-                const float li = r_lse[sl];
+#pragma unroll
+            for (int src = 0; src < XCHG_MAX_WORLD; ++src) {
+                if (src >= p.x_world) break;
+                const float li = x_lse[src];
                 if (li == -CUDART_INF_F) continue;
                 const float wgt_s = __expf(li - mx);
                 z += wgt_s;
-                const float2 ov = *reinterpret_cast<const float2*>(r_out + sl * HD + d);
-                b0 = fmaf(wgt_s, ov.x, b0);
-                b1 = fmaf(wgt_s, ov.y, b1);
+                b0 = fmaf(wgt_s, rv[src].x, b0);
+                b1 = fmaf(wgt_s, rv[src].y, b1);
             }
             b0 /= z;
             b1 /= z;

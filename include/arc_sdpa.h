@@ -150,17 +150,18 @@ typedef struct arc_sdpa_decode_params {
     int32_t num_ctas; /* 0 -> one per SM */
     void* workspace;
     size_t workspace_bytes;
-    /* Sequence-sharded decode over NVLink peer memory (optional; xchg_world <= 1: off).
+    /* Sequence-sharded decode over NVLink peer memory (optional; xchg_world <= 1: off; at most 16 ranks).
      * Each of xchg_world ranks (one process per GPU) holds a slice of every sequence's keys and
-     * calls this function with the same batch / heads and the same xchg_step, which must grow
-     * by one per call.  A rank whose slice is empty still takes part: kv_rows_total 0 with
-     * kv_len NULL and kv_len_uniform 0 sends records with lse = -inf.  xchg_peers: DEVICE array of xchg_world addresses, entry r = base of rank
-     * r's exchange buffer of arc_sdpa_exchange_bytes() bytes, mapped into this process (peer
-     * access / symmetric memory), zero-filled before the first step.  The merge kernel stores
-     * this rank's (out, lse) records into every rank's buffer, then waits — bounded, about a
-     * second, after which ARC_ERR_DEVICE_WAIT_TIMEOUT shows in arc_sdpa_device_status() — for
-     * all ranks' records and writes the merged (and gated) result to `out`.  `out_f32` /
-     * `out_lse`, if given, still receive this rank's own partial. */
+     * calls this function with the same batch / heads and the same xchg_step, which starts at 1 and
+     * must grow by one per call.  A rank whose slice is empty still takes part: kv_rows_total 0 with
+     * kv_len NULL and kv_len_uniform 0 sends records with lse = -inf.  xchg_peers: DEVICE array of
+     * xchg_world addresses, entry r = base of rank r's exchange buffer of arc_sdpa_exchange_bytes()
+     * bytes, mapped into this process (peer access / symmetric memory), zero-filled before the first
+     * step.  The merge kernel stores this rank's (out, lse) record into every rank's buffer as 8-byte
+     * (value, step) words — a receiver recognises each word by its step, so no flag or fence follows
+     * the data — then waits, bounded (about a second, after which ARC_ERR_DEVICE_WAIT_TIMEOUT shows in
+     * arc_sdpa_device_status()), for the words of all ranks and writes the merged (and gated) result
+     * to `out`.  `out_f32` / `out_lse`, if given, still receive this rank's own partial. */
     const uint64_t* xchg_peers;
     int32_t xchg_world, xchg_rank;
     uint32_t xchg_step;

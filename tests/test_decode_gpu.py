@@ -203,6 +203,38 @@ def test_peer_wait_gives_up_with_a_status_and_the_device_stays_usable(ops):
     assert_close(got[0], wf[0], "decode after the status was cleared")
 
 
+def test_exchange_fold_with_the_other_ranks_record_already_in_place(ops):
+    """The cross-rank fold of the sequence-sharded decode on one GPU, without two kernels waiting for each
+    other: "rank 1"'s record is computed first (return_partial) and written into rank 0's exchange buffer
+    in the wire format — 8-byte (value, step) words, log-sum-exp in word hd — then rank 0's call finds it
+    there, never waits, and must produce the attention over both halves of the keys, gate included."""
+    B, nq, nkv, hd, n, step = 2, 8, 2, 128, 700, 5
+    q, k, v = seeded_bf16(B, nq, hd, seed=91), seeded_bf16(B, n, nkv, hd, seed=92), seeded_bf16(B, n, nkv, hd, seed=93)
+    gate = seeded_bf16(B, nq, hd, seed=94)
+    qd, kd, vd, gd = q.cuda(), k.cuda(), v.cuda(), gate.cuda()
+    half = 384
+    _, o1, l1 = ops.sdpa_decode(qd, kd[:, half:].contiguous(), vd[:, half:].contiguous(), scale=hd ** -0.5, return_partial=True)
+    rows, words = B * nq, hd + 2
+    assert ops.exchange_bytes(2, B, nq, hd) == 2 * 2 * rows * words * 8
+    xbuf = torch.zeros(2, 2, rows, words, 2, dtype=torch.int32, device="cuda")  # [parity][source][row][word][value, step]
+    rec = xbuf[step & 1, 1]
+    rec[:, :hd, 0] = o1.reshape(rows, hd).contiguous().view(torch.int32)
+    rec[:, hd, 0] = l1.reshape(rows).contiguous().view(torch.int32)
+    rec[:, :, 1] = step
+    scratch = torch.zeros_like(xbuf)  # where rank 0's words for "rank 1" go
+    peers = torch.tensor([xbuf.data_ptr(), scratch.data_ptr()], dtype=torch.int64, device="cuda")
+    out = ops.sdpa_decode(qd, kd[:, :half].contiguous(), vd[:, :half].contiguous(), scale=hd ** -0.5, gate=gd,
+                          exchange=(peers, 2, 0, step), exchange_wait_cycles=20_000_000)
+    assert ops.device_status() == (0, 0)
+    whole = ops.sdpa_decode(qd, kd, vd, scale=hd ** -0.5, gate=gd)
+    assert_close(out, whole.float(), "two halves folded vs one pass", rel_tol=4e-3, abs_tol=2e-3)
+    for b in range(B):
+        _, want, _ = oracle.sdpa_f32(q[b:b + 1], k[b], v[b], scale=hd ** -0.5, gate=gate[b:b + 1], want_lse=True)
+        assert_close(out[b], want[0].float(), f"sequence {b}")
+    # rank 0's own words went out to both buffers, tagged with the step
+    assert (xbuf[step & 1, 0, :, :, 1] == step).all() and (scratch[step & 1, 0, :, :, 1] == step).all()
+
+
 def test_device_side_length_past_the_cache_is_a_status_not_a_wrong_result(ops):
     from arcaine_b200 import _lib
     B, nq, nkv, hd, cap = 2, 8, 2, 128, 64
