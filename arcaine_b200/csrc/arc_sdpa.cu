@@ -37,7 +37,9 @@ struct DeviceState {
     int sm_count = 0;
     int smem_optin = 0;
     // largest cluster size (2, 4 or 8; 0 = none) the cluster form of the prefill kernel can be launched with, per head dim
-    int max_cluster[2] = {0, 0};
+    // [head dim 128 / 256][log2(cluster size)]: how many clusters of 2, 4, 8 CTAs of the cluster form of the
+    // prefill kernel the device can hold at once (0: that size cannot be launched)
+    int active_clusters[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 };
 
 static DeviceState g_dev[kMaxDevices];
@@ -105,9 +107,9 @@ static int device_state(DeviceState** out) {
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, false, true>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, false, true>, PrefillCfg<256>::SMEM_BYTES));
             for (int hi = 0; hi < 2; ++hi) {
-                for (int cs = 2; cs <= 8; cs *= 2) {
+                for (int cs = 2, lg = 1; cs <= 8; cs *= 2, ++lg) {
                     cudaLaunchConfig_t cfg{};
-                    cfg.gridDim = dim3((unsigned)cs);
+                    cfg.gridDim = dim3((unsigned)(s.sm_count / cs * cs));  // the answer is capped by the grid asked about
                     cfg.blockDim = dim3(hi ? PrefillCfg<256>::THREADS : PrefillCfg<128>::THREADS);
                     cfg.dynamicSmemBytes = hi ? PrefillCfg<256>::SMEM_BYTES : PrefillCfg<128>::SMEM_BYTES;
                     cudaLaunchAttribute attr[1];
@@ -120,7 +122,7 @@ static int device_state(DeviceState** out) {
                     int n = 0;
                     const cudaError_t e = hi ? cudaOccupancyMaxActiveClusters(&n, sdpa_prefill_kernel<256, false, false, true>, &cfg)
                                              : cudaOccupancyMaxActiveClusters(&n, sdpa_prefill_kernel<128, false, false, true>, &cfg);
-                    if (e == cudaSuccess && n > 0) s.max_cluster[hi] = cs;
+                    if (e == cudaSuccess && n > 0) s.active_clusters[hi][lg] = n;
                     else cudaGetLastError();
                 }
             }
@@ -206,7 +208,7 @@ struct PrefillPlan {
     size_t ws_bytes = 0;     // all of the workspace: partial records, then the per-row span ends of block_ids
 };
 
-static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, int max_cluster, PrefillPlan* plan) {
+static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, const int* active_clusters, PrefillPlan* plan) {
     if (!p) return ARC_ERR_NULL_POINTER;
     if (p->batch <= 0 || p->seq <= 0 || p->kv_len <= 0 || p->nq <= 0 || p->nkv <= 0 || p->nq % p->nkv != 0)
         return ARC_ERR_BAD_SHAPE;
@@ -219,9 +221,9 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, int max_
     plan->rows = (long long)p->batch * p->seq * p->nq;
     const int kv_blocks = (p->kv_len + 127) / 128;
     int splits = p->num_splits;
+    const long long tiles = (long long)plan->q_tiles * p->nq * p->batch;
     if (splits == 0) {
         // Split the key range only when the tiles alone leave most SMs idle.
-        const long long tiles = (long long)plan->q_tiles * p->nq * p->batch;
         splits = 1;
         if (tiles * 2 <= sm_count && kv_blocks >= 4) {
             splits = (int)(sm_count / tiles);
@@ -234,11 +236,17 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, int max_
     // A split the library chose itself is run as a thread-block cluster where the device allows it: the
     // CTAs of a tile fold their accumulators through distributed shared memory in the same launch, no
     // partial records, no merge kernel, no workspace.  An explicit num_splits keeps the two-launch form.
-    if (p->num_splits == 0 && splits > 1 && max_cluster >= 2 && p->mask_type != ARC_MASK_EXPLICIT) {
-        int cs = 2;
-        while (cs * 2 <= splits && cs * 2 <= max_cluster) cs *= 2;
-        plan->cluster = cs;
-        splits = 1;
+    // The cluster size is the largest power of two within the split count for which all tiles' clusters
+    // are resident at once (clusters are placed inside one GPC each, so fewer fit than SMs / size suggests;
+    // a second wave would double the time).
+    if (p->num_splits == 0 && splits > 1 && active_clusters && p->mask_type != ARC_MASK_EXPLICIT) {
+        int cs = 0;
+        for (int c = 2, lg = 1; c <= 8 && c <= splits; c *= 2, ++lg)
+            if (active_clusters[lg] >= tiles) cs = c;
+        if (cs > 0) {
+            plan->cluster = cs;
+            splits = 1;
+        }
     }
     plan->splits = splits;
     plan->split_bytes = splits > 1 ? (size_t)splits * plan->rows * ((size_t)p->hd + 1) * sizeof(float) : 0;
@@ -340,9 +348,7 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         if (tiles > 0x7fffffffLL) return ARC_ERR_TOO_LARGE;
         kp.total_tiles = (int)tiles;
         kp.num_splits = 1;
-        long long nclusters = ds->sm_count / plan.cluster;
-        if (nclusters > tiles) nclusters = tiles;
-        if (nclusters < 1) nclusters = 1;
+        const long long nclusters = tiles;  // the plan made sure that many are resident at once
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3((unsigned)(nclusters * plan.cluster));
         cfg.blockDim = dim3(PrefillCfg<HD>::THREADS);
@@ -564,7 +570,7 @@ extern "C" size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params
     int sm = 148;
     if (device_state(&ds) == ARC_OK) sm = ds->sm_count;
     PrefillPlan plan;
-    if (plan_prefill(p, sm, ds ? ds->max_cluster[p && p->hd == 256 ? 1 : 0] : 0, &plan) != ARC_OK) return 0;
+    if (plan_prefill(p, sm, ds ? ds->active_clusters[p && p->hd == 256 ? 1 : 0] : nullptr, &plan) != ARC_OK) return 0;
     return plan.ws_bytes;
 }
 
@@ -576,7 +582,7 @@ extern "C" int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream) 
     int rc = device_state(&ds);
     if (rc != ARC_OK) return rc;
     PrefillPlan plan;
-    if ((rc = plan_prefill(p, ds->sm_count, ds->max_cluster[p->hd == 256 ? 1 : 0], &plan)) != ARC_OK) return rc;
+    if ((rc = plan_prefill(p, ds->sm_count, ds->active_clusters[p->hd == 256 ? 1 : 0], &plan)) != ARC_OK) return rc;
     if (!aligned16(p->q) || !aligned16(p->k) || !aligned16(p->v) || !aligned16(p->out) ||
         (p->gate && !aligned16(p->gate)))
         return ARC_ERR_ALIGNMENT;
