@@ -55,6 +55,7 @@ class PrefillParams(C.Structure):
         ("scale", C.c_float), ("mask_type", C.c_int32), ("window", C.c_int32), ("num_splits", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("block_ids", C.c_void_p), ("block_ids_offset", C.c_int32),
+        ("out_copies", C.c_void_p), ("out_copy_count", C.c_int32),
     ]
 
 

@@ -270,6 +270,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
 
     PrefillParams kp{};
     kp.out = static_cast<uint16_t*>(p->out);
+    kp.out_copies = reinterpret_cast<const unsigned long long*>(p->out_copies);
+    kp.n_copies = p->out_copies ? p->out_copy_count : 0;
     kp.gate = static_cast<const uint16_t*>(p->gate);
     kp.mask = p->mask_type == ARC_MASK_EXPLICIT ? p->mask : nullptr;
     kp.out_lse = p->out_lse;
@@ -396,6 +398,8 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         mp.nq = p->nq;
         mp.o_stride_b = p->o_stride_b;
         mp.o_stride_t = p->o_stride_t;
+        mp.out_copies = kp.out_copies;
+        mp.n_copies = kp.n_copies;
         ARC_CUDA(launch_dependent(sdpa_uniform_merge_kernel<HD>, dim3((unsigned)((plan.rows + UMERGE_ROWS - 1) / UMERGE_ROWS)),
                                   dim3(32 * UMERGE_ROWS), 0, stream, mp));
         g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -578,6 +582,7 @@ extern "C" int arc_sdpa_prefill(const arc_sdpa_prefill_params* p, void* stream) 
     if (!p) return ARC_ERR_NULL_POINTER;
     if (!p->q || !p->k || !p->v || !p->out) return ARC_ERR_NULL_POINTER;
     if (p->mask_type == ARC_MASK_EXPLICIT && !p->mask) return ARC_ERR_NULL_POINTER;
+    if (p->out_copy_count < 0 || p->out_copy_count > 15 || (p->out_copy_count > 0 && !p->out_copies)) return ARC_ERR_BAD_SHAPE;
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc != ARC_OK) return rc;

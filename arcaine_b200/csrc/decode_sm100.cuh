@@ -697,6 +697,8 @@ struct UniformMergeParams {
     int num_parts;
     int seq, nq;  // seq > 0: strided (b, t, h) addressing of out / gate
     long long o_stride_b, o_stride_t;
+    const unsigned long long* out_copies;  // n_copies more output buffers, same offsets (prefill: other GPUs' buffers)
+    int n_copies;
 };
 
 constexpr int UMERGE_ROWS = 8;  // rows per block of the uniform merge: one warp each
@@ -784,8 +786,11 @@ __global__ void __launch_bounds__(32 * UMERGE_ROWS) sdpa_uniform_merge_kernel(co
             }
             packed[j] = pack_bf16x2(a0, a1);
         }
-        if (VPL == 8) *reinterpret_cast<uint4*>(p.out + eoff) = make_uint4(packed[0], packed[1], packed[VPL / 2 - 2], packed[VPL / 2 - 1]);
-        else *reinterpret_cast<uint2*>(p.out + eoff) = make_uint2(packed[0], packed[1]);
+        for (int c = -1; c < p.n_copies; ++c) {
+            uint16_t* o = (c < 0 ? p.out : reinterpret_cast<uint16_t*>(p.out_copies[c])) + eoff;
+            if (VPL == 8) *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[VPL / 2 - 2], packed[VPL / 2 - 1]);
+            else *reinterpret_cast<uint2*>(o) = make_uint2(packed[0], packed[1]);
+        }
     }
 }
 

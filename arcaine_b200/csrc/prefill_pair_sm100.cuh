@@ -434,8 +434,10 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                 if (pw.hi_of(s) == pw.lo_of(s)) {
                     // Nothing visible for this tile: zero output.
                     if (store) {
-                        uint4* dst = reinterpret_cast<uint4*>(p.out + eoff);
-                        for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = -1; c < p.n_copies; ++c) {
+                            uint4* dst = reinterpret_cast<uint4*>((c < 0 ? p.out : reinterpret_cast<uint16_t*>(p.out_copies[c])) + eoff);
+                            for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        }
                         if (p.out_lse) p.out_lse[row] = -CUDART_INF_F;
                     }
                     continue;
@@ -459,7 +461,6 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                 const uint32_t tO = tmem_base + lane_sel + C::COL_O + s * 128;
                 uint16_t* dst = p.out + eoff;
                 const uint16_t* gp = GATE ? p.gate + eoff : nullptr;
-                const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
 #pragma unroll
                 for (int c = 0; c < HD / 32; ++c) {
                     tmem_ld32(tO + c * 32, wa);
@@ -488,15 +489,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                                     w8[u] = pack_bf16x2(a0 * (1.0f / (1.0f + __expf(-g0f))), a1 * (1.0f / (1.0f + __expf(-g1f))));
                                 }
                             }
-                            uint16_t* q = dst + c * 32 + i * 16;
-                            if (wide) {
-                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(w8[0]),
-                                             "r"(w8[1]), "r"(w8[2]), "r"(w8[3]), "r"(w8[4]), "r"(w8[5]), "r"(w8[6]), "r"(w8[7])
-                                             : "memory");
-                            } else {
-                                *reinterpret_cast<uint4*>(q) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
-                                *reinterpret_cast<uint4*>(q + 8) = make_uint4(w8[4], w8[5], w8[6], w8[7]);
-                            }
+                            store_bf16x16(dst + c * 32 + i * 16, w8);
+                            if (p.n_copies) store_copies_bf16x16(p.out_copies, p.n_copies, eoff + c * 32 + i * 16, w8);
                         }
                     }
                 }

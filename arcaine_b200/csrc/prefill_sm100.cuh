@@ -33,6 +33,8 @@ namespace arc {
 
 struct PrefillParams {
     uint16_t* out;
+    const unsigned long long* out_copies;  // n_copies more output buffers (other GPUs' over NVLink), same offsets
+    int n_copies;
     const uint16_t* gate;
     const float* mask;
     float* out_lse;
@@ -107,6 +109,26 @@ __device__ __forceinline__ float masked_score(uint32_t raw, float sl, int key, c
         if (rm.mask_row && key < rm.kv_len) x += rm.mask_row[key] * 1.4426950408889634f;
     }
     return (key >= rm.lo && key < rm.hi) ? x : -CUDART_INF_F;
+}
+
+// 32 bytes (16 bf16) to q: one 256-bit store where q is 32-byte aligned (a whole DRAM sector), else two
+// 128-bit stores.
+__device__ __forceinline__ void store_bf16x16(uint16_t* q, const uint32_t (&w)[8]) {
+    if ((reinterpret_cast<uintptr_t>(q) & 31u) == 0) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                     "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
+    } else {
+        *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(q + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
+// The same 32 bytes at element offset `off` of every copy of the output (plain stores; a copy in another
+// GPU's memory travels over NVLink while the kernel computes on).
+__device__ __forceinline__ void store_copies_bf16x16(const unsigned long long* copies, int n, long long off,
+                                                     const uint32_t (&w)[8]) {
+    for (int c = 0; c < n; ++c) store_bf16x16(reinterpret_cast<uint16_t*>(copies[c]) + off, w);
 }
 
 // bf16(attention) * sigmoid(gate), the rounding order of mul_sigmoid_inplace after a bf16 attention
@@ -655,8 +677,10 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                         o4[2] = sigmoid_gate_bits(o4[2], (uint16_t)(gv[b].y & 0xffffu));
                         o4[3] = sigmoid_gate_bits(o4[3], (uint16_t)(gv[b].y >> 16));
                     }
-                    *reinterpret_cast<uint2*>(p.out + eoff + (lane + 32 * j) * 4) =
-                        make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3]));
+                    const uint2 packed = make_uint2(pack_bf16x2(o4[0], o4[1]), pack_bf16x2(o4[2], o4[3]));
+                    *reinterpret_cast<uint2*>(p.out + eoff + (lane + 32 * j) * 4) = packed;
+                    for (int c = 0; c < p.n_copies; ++c)
+                        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out_copies[c]) + eoff + (lane + 32 * j) * 4) = packed;
                     if (j == 0 && lane == 0 && p.out_lse)
                         p.out_lse[((long long)tw.b * p.seq + tt) * p.nq + tw.h] =
                             ltot > 0.f ? (mx + fast_log2(ltot)) * 0.6931471805599453f : -CUDART_INF_F;
@@ -740,9 +764,11 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                         for (int i = 0; i < OC / 4; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (kh == 0) p.part_lse[(long long)tw.split * rows_total + row] = -CUDART_INF_F;
                     } else {
-                        uint4* dst = reinterpret_cast<uint4*>(p.out + tw.b * p.o_stride_b + t * p.o_stride_t +
-                                                              (long long)tw.h * HD + kh * OC);
-                        for (int i = 0; i < OC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        const long long zoff = tw.b * p.o_stride_b + t * p.o_stride_t + (long long)tw.h * HD + kh * OC;
+                        for (int c = -1; c < p.n_copies; ++c) {
+                            uint4* dst = reinterpret_cast<uint4*>((c < 0 ? p.out : reinterpret_cast<uint16_t*>(p.out_copies[c])) + zoff);
+                            for (int i = 0; i < OC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                        }
                         if (kh == 0 && p.out_lse) p.out_lse[row] = -CUDART_INF_F;
                     }
                 }
@@ -983,9 +1009,7 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 const long long eoff = tw.b * p.o_stride_b + t * p.o_stride_t + (long long)tw.h * HD + kh * OC;
                 uint16_t* dst = p.out + eoff;
                 const uint16_t* gp = (GATE && p.gate) ? p.gate + eoff : nullptr;
-                // One thread writes 128 (or 256) contiguous bytes of its row.  When the row is 32-byte
-                // aligned this goes out as 256-bit stores, each a whole DRAM sector.
-                const bool wide = (reinterpret_cast<uintptr_t>(dst) & 31u) == 0;
+                // One thread writes 128 (or 256) contiguous bytes of its row.
 #pragma unroll 1
                 for (int c = 0; c < OC / 32; ++c) {
                     tmem_ld32(tO + c * 32, va);
@@ -1016,15 +1040,8 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
 #pragma unroll
                                 for (int u = 0; u < 4; ++u) ov[hh * 4 + u] = pack_bf16x2(o[2 * u], o[2 * u + 1]);
                             }
-                            uint16_t* q = dst + c * 32 + e;
-                            if (wide) {
-                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(q), "r"(ov[0]),
-                                             "r"(ov[1]), "r"(ov[2]), "r"(ov[3]), "r"(ov[4]), "r"(ov[5]), "r"(ov[6]), "r"(ov[7])
-                                             : "memory");
-                            } else {
-                                *reinterpret_cast<uint4*>(q) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                                *reinterpret_cast<uint4*>(q + 8) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
-                            }
+                            store_bf16x16(dst + c * 32 + e, ov);
+                            if (p.n_copies) store_copies_bf16x16(p.out_copies, p.n_copies, eoff + c * 32 + e, ov);
                         }
                     }
                 }

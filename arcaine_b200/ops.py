@@ -75,13 +75,17 @@ def sdpa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: fl
                  gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                  num_splits: int = 0, return_lse: bool = False,
                  workspace: Optional[Workspace] = None,
-                 block_ids: Optional[torch.Tensor] = None, block_ids_offset: int = 0):
+                 block_ids: Optional[torch.Tensor] = None, block_ids_offset: int = 0,
+                 out_copies: Optional[torch.Tensor] = None):
     """Prefill / canvas attention.  q: (B, S, nq, hd) or (S, nq, hd); k, v: (B, L, nkv, hd) or (L, nkv, hd).
 
     ``out`` may be ``q`` itself.  Returns ``out`` (and the natural-log LSE (B, S, nq) when asked).
     ``block_ids`` (device int32, one per absolute position, -1 = text; causal masks only): Gemma4's
     vision blocks — a query inside a block also sees the block's later keys
     (src/common/kernels/attention_mask.hpp:44-73); ``block_ids[block_ids_offset + j]`` is key j's id.
+    ``out_copies`` (device int64, at most 15 addresses): further buffers laid out like ``out`` that the
+    kernel's epilogue stores the result to as well — other GPUs' mapped buffers when a head-sharded output
+    is to be gathered (see ``sharded.GatheredPrefill``).
     """
     squeeze = q.dim() == 3
     if squeeze:
@@ -124,6 +128,11 @@ def sdpa_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: fl
         if not block_ids.is_contiguous() or block_ids.numel() < block_ids_offset + L or block_ids_offset < 0:
             raise ValueError("block_ids must be contiguous and hold block_ids_offset + kv_len entries")
         p.block_ids, p.block_ids_offset = block_ids.data_ptr(), int(block_ids_offset)
+    if out_copies is not None:
+        _require(out_copies, torch.int64, "out_copies")
+        if not out_copies.is_contiguous() or out_copies.numel() > 15:
+            raise ValueError("out_copies must be a contiguous int64 tensor of at most 15 addresses")
+        p.out_copies, p.out_copy_count = out_copies.data_ptr(), out_copies.numel()
     L_ = _lib.load()
     with torch.cuda.device(q.device):
         need = L_.arc_sdpa_prefill_workspace_bytes(C.byref(p))

@@ -165,8 +165,9 @@ class SeqShardedDecode:
 
     * ``peer`` (default when symmetric memory can be set up): two launches per step.  The decode
       merge kernel stores this rank's ``(out, lse)`` records straight into every rank's exchange
-      buffer over NVLink, raises a per-row flag there, waits (bounded) for all ranks' flags for
-      its rows and folds the records — the exchange is part of the kernel, no collective call.
+      buffer over NVLink as (value, step) words, waits (bounded) until the words of all ranks for
+      its rows show the step, and folds the records — the exchange is part of the kernel, no
+      collective call.
     * ``nccl``: local decode writes the packed record, one ``all_gather_into_tensor`` moves it,
       the uniform merge kernel folds the gathered records in place.
     """
@@ -232,6 +233,51 @@ class SeqShardedDecode:
             dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
             return ops.sdpa_merge(self.all_out, self.all_lse, gate=gate, out=self.out)
         return ops.sdpa_merge(self.part_out.unsqueeze(0), self.part_lse.unsqueeze(0), gate=gate, out=self.out)
+
+
+class GatheredPrefill:
+    """Head/batch-sharded prefill whose output every rank ends up holding whole, without a collective:
+    the gather buffer ``(world, *out_local.shape)`` lives in symmetric memory, and the prefill kernel's
+    epilogue stores this rank's slice into slot ``rank`` of every rank's buffer (its own directly, the
+    others' through their mapped addresses over NVLink) while it computes.  A rank's slice is in place
+    everywhere once its call has completed; ``wait_all()`` is the cross-rank barrier a consumer needs
+    before it reads the other slots."""
+
+    def __init__(self, out_local_shape, device: torch.device, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        shape = (self.world,) + tuple(out_local_shape)
+        numel = 1
+        for s in shape:
+            numel *= s
+        self.copies = None
+        if self.world > 1:
+            flat = symm_mem.empty(numel, dtype=torch.bfloat16, device=device)
+            hdl = symm_mem.rendezvous(flat, group if group is not None else dist.group.WORLD)
+            ptrs = [int(x) for x in hdl.buffer_ptrs]
+            if len(ptrs) != self.world:
+                raise RuntimeError("symmetric memory rendezvous returned an unexpected number of peers")
+            slot_bytes = (numel // self.world) * 2
+            self.copies = torch.tensor([ptrs[r] + self.rank * slot_bytes for r in range(self.world) if r != self.rank],
+                                       dtype=torch.int64, device=device)
+            self._flat, self._hdl = flat, hdl
+        else:
+            flat = torch.empty(numel, dtype=torch.bfloat16, device=device)
+        self.gathered = flat.view(shape)
+
+    def __call__(self, q_local, k_local, v_local, *, scale, mask_type, window, gate_local=None):
+        from . import ops
+        return ops.sdpa_prefill(q_local, k_local, v_local, scale=scale, mask_type=mask_type, window=window,
+                                gate=gate_local, out=self.gathered[self.rank], out_copies=self.copies)
+
+    def wait_all(self):
+        """Every rank's slice has landed in this rank's buffer (host-side: stream sync + barrier)."""
+        torch.cuda.current_stream().synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        return self.gathered
 
 
 def prefill_head_sharded(q_local, k_local, v_local, *, scale, mask_type, window, gate_local=None, out_local=None,

@@ -569,6 +569,30 @@ class PrefillWindowGathered(PrefillWindow):
         return c
 
 
+class PrefillWindowPeerGathered(PrefillWindow):
+    """Config 3 with the output gather inside the kernel: the epilogue stores every output row into every
+    rank's gather buffer (symmetric memory, plain peer stores over NVLink), so the transfer overlaps the
+    attention tile by tile and no collective follows."""
+    name = "prefill_window_peer_gathered"
+
+    def __init__(self, rank, world, device, pin=False):
+        super().__init__(rank, world, device, pin=False)
+        from arcaine_b200 import sharded
+        self.runner = sharded.GatheredPrefill(tuple(self.out.shape), device)
+
+    def working_set_bytes(self):
+        return (self.q.numel() + self.k.numel() + self.v.numel() + self.runner.gathered.numel()) * 2
+
+    def step(self):
+        self.runner(self.q, self.k, self.v, scale=self.scale, mask_type=self.ops.MASK_CAUSAL, window=CFG3["W"])
+
+    def config(self):
+        c = super().config()
+        c["partition"] = c["partition"].replace("output stays head-sharded",
+                                                "output rows stored into every rank's buffer by the kernel's epilogue (peer stores over NVLink)")
+        return c
+
+
 WORKLOADS = {w.name: w for w in (PrefillWindow, Canvas, DecodeGated, DecodeLong, QkvPrepare)}
 
 
@@ -953,12 +977,13 @@ def main():
             except Exception as e:  # an extra never takes the headline down
                 extra[name] = {"error": repr(e)}
         if world > 1 and args.workload == "prefill_window":
-            try:
-                r = measure(PrefillWindowGathered, runner, max(5, min(args.steps, 20)), 3, peaks, traffic,
-                            with_e2e=False, sample_clocks=False)
-                extra["prefill_window_gathered"] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "roofline", "config", "timing")}
-            except Exception as e:
-                extra["prefill_window_gathered"] = {"error": repr(e)}
+            for cls in (PrefillWindowGathered, PrefillWindowPeerGathered):
+                try:
+                    r = measure(cls, runner, max(5, min(args.steps, 20)), 3, peaks, traffic,
+                                with_e2e=False, sample_clocks=False)
+                    extra[cls.name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "roofline", "config", "timing")}
+                except Exception as e:
+                    extra[cls.name] = {"error": repr(e)}
     parity = None
     if world > 1:
         try:

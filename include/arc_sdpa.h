@@ -103,6 +103,16 @@ typedef struct arc_sdpa_prefill_params {
      * workspace (arc_sdpa_prefill_workspace_bytes()); head dim 128 then runs the one-tile kernel. */
     const int32_t* block_ids;
     int32_t block_ids_offset;
+    /* Copies of the output (optional; no counterpart in the reference, which is single-device).
+     * out_copies: DEVICE array of out_copy_count (<= 15) addresses; every output element is stored to
+     * `out` and, at the same element offset, to each of them by the kernel's own epilogue.  With a
+     * head-sharded prefill over several GPUs the entries are the other ranks' mapped output buffers
+     * (peer access / symmetric memory), offset to this rank's head slice: the output gather then rides
+     * on the kernel's stores over NVLink while it computes, instead of a collective after it.  The
+     * copies are complete when the call has completed on its stream; telling the other ranks is the
+     * caller's business (a barrier, a flag).  Entries must be 16-byte aligned; lse is not copied. */
+    const uint64_t* out_copies;
+    int32_t out_copy_count;
 } arc_sdpa_prefill_params;
 
 size_t arc_sdpa_prefill_workspace_bytes(const arc_sdpa_prefill_params* p);

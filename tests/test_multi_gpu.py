@@ -117,6 +117,23 @@ def _rank_main(rank, world, port):
         if rank == 0:
             want, _ = oracle.sdpa_f32(qp, k[0, :S], v[0, :S], scale=scale, mask_type=3, window=100)
             assert_close(torch.cat(list(parts), dim=1), want, "gathered head shards")
+        # the same gather done by the kernel's own epilogue: every rank's rows stored into every rank's
+        # buffer over NVLink (symmetric memory), no collective; a large case as well, so that both prefill
+        # kernels take part
+        for S2, win in ((300, 100), (2048, 512)):
+            q2 = seeded_bf16(S2, nq, hd, seed=6)
+            args = (q2[:, sh.q_head_begin:sh.q_head_end].contiguous().to(dev),
+                    k[0, :S2, sh.kv_head_begin:sh.kv_head_end].contiguous().to(dev),
+                    v[0, :S2, sh.kv_head_begin:sh.kv_head_end].contiguous().to(dev))
+            ref = ops.sdpa_prefill(*args, scale=scale, mask_type=ops.MASK_CAUSAL, window=win)
+            gp = sharded.GatheredPrefill(tuple(ref.shape), dev)
+            local = gp(*args, scale=scale, mask_type=ops.MASK_CAUSAL, window=win)
+            both = gp.wait_all()
+            assert torch.equal(local, ref) and torch.equal(both[rank], ref)
+            theirs = [torch.empty_like(ref) for _ in range(world)]
+            dist.all_gather(theirs, ref)
+            for r in range(world):
+                assert torch.equal(both[r], theirs[r]), f"slot {r} of rank {rank}'s buffer (S {S2})"
         dist.barrier()
     finally:
         dist.destroy_process_group()

@@ -102,6 +102,36 @@ def test_cluster_fold_of_key_range_splits(ops, hd, seq, kv_len, nq, nkv, mask_ty
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=600 + hd + seq)
 
 
+@pytest.mark.parametrize("case", ["pair", "single", "cluster", "two_launch", "nothing_visible"])
+def test_output_copies_are_written_by_every_epilogue(ops, case):
+    """out_copies: further buffers that receive the same rows at the same offsets (other GPUs' buffers when
+    a head-sharded output is gathered; here two more buffers on the same device), through every kernel
+    that writes output."""
+    seq, kv, nq, nkv, hd, mask, win, splits = {
+        "pair": (1024, 1024, 8, 4, 128, 3, 256, 0),          # enough tiles for the two-tile kernel
+        "single": (300, 300, 4, 2, 256, 3, oracle.INT_MAX, 1),
+        "cluster": (256, 1200, 4, 2, 256, 0, oracle.INT_MAX, 0),
+        "two_launch": (256, 1200, 4, 2, 128, 0, oracle.INT_MAX, 3),
+        "nothing_visible": (200, 100, 4, 2, 128, 3, oracle.INT_MAX, 0),  # the first 100 queries see no key
+    }[case]
+    q, k, v = seeded_bf16(seq, nq, hd, seed=700), seeded_bf16(kv, nkv, hd, seed=701), seeded_bf16(kv, nkv, hd, seed=702)
+    g = seeded_bf16(seq, nq, hd, seed=703)
+    plain = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, mask_type=mask, window=win,
+                             num_splits=splits, gate=g.cuda())
+    # the copies sit inside a wider buffer (a head slice of a full-width output), like the gathered layout
+    wide = [torch.full((seq, 2 * nq, hd), 9.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    out = torch.empty(seq, 2 * nq, hd, dtype=torch.bfloat16, device="cuda")[:, nq:]
+    copies = torch.tensor([w[:, nq:].data_ptr() for w in wide], dtype=torch.int64, device="cuda")
+    gate_wide = torch.empty(seq, 2 * nq, hd, dtype=torch.bfloat16, device="cuda")[:, nq:]  # laid out like out
+    gate_wide.copy_(g)
+    got = ops.sdpa_prefill(q.cuda(), k.cuda(), v.cuda(), scale=hd ** -0.5, mask_type=mask, window=win,
+                           num_splits=splits, gate=gate_wide, out=out, out_copies=copies)
+    torch.cuda.synchronize()
+    assert torch.equal(got, plain)
+    for w in wide:
+        assert torch.equal(w[:, nq:], plain) and (w[:, :nq].float() == 9.0).all()
+
+
 def test_gate_epilogue_and_split_gate(ops):
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True)
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True, num_splits=2)
