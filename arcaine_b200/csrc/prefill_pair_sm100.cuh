@@ -650,7 +650,15 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                 mbar_arrive(&turn[s]);
                 if (act && j + 1 == hi) {
                     // The tile's last key block is on its way: hand the row sum and maximum to the
-                    // epilogue warps and go on with the next tile.
+                    // epilogue warps and go on with the next tile.  Not before the epilogue has taken the
+                    // previous tile, though: a tile of one key block needs no O += P V to get here, so these
+                    // warps could complete `fin` twice while a slow epilogue (its stores held up) still waits
+                    // for the first completion — which a parity wait can then no longer tell from "not yet".
+                    if (tq > 0 && !mbar_wait_warp<3>(&o_empty[s], (tq - 1) & 1)) {
+                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x600u + s);
+                        ok = false;
+                        break;
+                    }
                     fin_vals[((tq & 1) * 2 + s) * 128 + r] = make_float2(l, m);
                     mbar_arrive(&fin[s]);
                     ++tq;

@@ -22,8 +22,10 @@ Workloads
 Every workload is timed two ways at every N: each step on its own pair of CUDA events after an L2
 flush (the reported number), and all steps back to back (under "timing").  With N > 1 the line
 also carries "parity": the sequence-sharded decode checked, outside every timed region, against a
-plain fp32 softmax on the device and against its NCCL form, and "prefill_window_gathered": config 3
-with the all-gather of the output slices inside the step.
+plain fp32 softmax on the device and against its NCCL form, and two more lines under "extra":
+"prefill_window_gathered" (config 3 with an NCCL all-gather of the output slices inside the step) and
+"prefill_window_peer_gathered" (the same gather done by the kernel's own epilogue stores into the
+other ranks' buffers over NVLink).
 
 --impl reference times the CPU port of the reference's matmul/softmax/matmul path
 (oracle/, all host threads) on a bounded sample of the same workload.
@@ -680,6 +682,7 @@ def measure(workload_cls, runner, steps, warmup, peaks, traffic, with_e2e=True, 
     launches_total = int(runner.sum_over_ranks(float(launches)))
     status = ops.device_status()
     if status != (0, 0):
+        ops.clear_device_status()  # re-arm the kernels: what follows (extras, parity) must not inherit it
         raise RuntimeError(f"device-side wait timed out during the bench: {status}")
     ms_step = ms / steps
     value = w.units_total() / (ms_step / 1e3)

@@ -102,13 +102,13 @@ def test_cluster_fold_of_key_range_splits(ops, hd, seq, kv_len, nq, nkv, mask_ty
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=600 + hd + seq)
 
 
-@pytest.mark.parametrize("case", ["pair", "single", "cluster", "two_launch", "nothing_visible"])
+@pytest.mark.parametrize("case", ["hd128", "single", "cluster", "two_launch", "nothing_visible"])
 def test_output_copies_are_written_by_every_epilogue(ops, case):
     """out_copies: further buffers that receive the same rows at the same offsets (other GPUs' buffers when
     a head-sharded output is gathered; here two more buffers on the same device), through every kernel
     that writes output."""
     seq, kv, nq, nkv, hd, mask, win, splits = {
-        "pair": (1024, 1024, 8, 4, 128, 3, 256, 0),          # enough tiles for the two-tile kernel
+        "hd128": (1024, 1024, 8, 4, 128, 3, 256, 0),         # (the two-tile kernel's copies: test_prefill_pair_gpu.py)
         "single": (300, 300, 4, 2, 256, 3, oracle.INT_MAX, 1),
         "cluster": (256, 1200, 4, 2, 256, 0, oracle.INT_MAX, 0),
         "two_launch": (256, 1200, 4, 2, 128, 0, oracle.INT_MAX, 3),

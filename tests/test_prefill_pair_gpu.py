@@ -73,6 +73,15 @@ from helpers import sample_rows
 rows = sample_rows(S, nq, 400, seed=77)
 want, _ = oracle.sdpa_f32(q[1].cpu(), k[1].cpu(), v[1].cpu(), scale=128 ** -0.5, mask_type=3, window=1024, rows=rows)
 assert_close(out[1].reshape(-1, 128)[rows], want, "batch 2 x 4096")
+# output copies from this kernel's epilogue, several units per CTA, tiles of a single key block among them
+# (S = 8192, window 1024: the first token tile of every head sees one block)
+q1, k1, v1 = q[:1].repeat(1, 2, 1, 1), k[:1].repeat(1, 2, 1, 1), v[:1].repeat(1, 2, 1, 1)
+ref = ops.sdpa_prefill(q1, k1, v1, scale=128 ** -0.5, mask_type=3, window=1024)
+bufs = [torch.zeros_like(ref) for _ in range(3)]
+copies = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device='cuda')
+got = ops.sdpa_prefill(q1, k1, v1, scale=128 ** -0.5, mask_type=3, window=1024, out_copies=copies)
+torch.cuda.synchronize()
+assert torch.equal(got, ref) and all(torch.equal(b, ref) for b in bufs), "output copies"
 assert ops.device_status() == (0, 0)
 assert ops.launch_count() > 0
 print("PAIR-OK")
