@@ -96,8 +96,10 @@ static int device_state(DeviceState** out) {
                 }
                 g_encode = reinterpret_cast<EncodeTiledFn>(fn);
             }
-            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<false>, PairCfg::SMEM_BYTES));
-            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<true>, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<false, false>, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<true, false>, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<false, true>, PairCfg::SMEM_BYTES));
+            ARC_CUDA(opt_in_smem(sdpa_prefill_pair_kernel<true, true>, PairCfg::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, false>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, true>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, true, true>, PrefillCfg<128>::SMEM_BYTES));
@@ -331,8 +333,14 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             kp.q_tiles = head_pair ? plan.q_tiles : (p->seq + 255) / 256;
             kp.total_tiles = (int)pair_tiles;
             const unsigned ctas = (unsigned)(pair_tiles < ds->sm_count ? pair_tiles : ds->sm_count);
-            if (kp.gate) sdpa_prefill_pair_kernel<true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
-            else sdpa_prefill_pair_kernel<false><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            if (kp.n_copies > 0) {
+                if (kp.gate) sdpa_prefill_pair_kernel<true, true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+                else sdpa_prefill_pair_kernel<false, true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            } else if (kp.gate) {
+                sdpa_prefill_pair_kernel<true, false><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            } else {
+                sdpa_prefill_pair_kernel<false, false><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
+            }
             g_launches.fetch_add(1, std::memory_order_relaxed);
             ARC_CUDA(cudaGetLastError());
             return ARC_OK;

@@ -48,8 +48,8 @@ struct PairCfg {
     static constexpr int COL_S = 0;    // + 128 * pipeline
     static constexpr int COL_O = 256;  // + 128 * pipeline
     // q_full[2] q_empty[2] k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] then per pipeline:
-    // s_full p_half[2] o_full o_empty turn fin
-    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 14;
+    // s_full p_half[2] o_full o_empty turn fin[2]
+    static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 16;
     static constexpr int FIN_FLOATS = 2 * 2 * 128 * 2;  // [tile parity][pipeline][row] (row sum, row maximum)
     static constexpr int SMEM_BYTES = (2 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + FIN_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;   // four per pipeline
@@ -144,7 +144,9 @@ __device__ __forceinline__ void mask_chunk(uint32_t (&v)[32], int key0, const Ro
     for (int e = 0; e < 32; ++e) v[e] = (static_cast<uint32_t>(e) - lo_rel < span) ? v[e] : 0xff800000u;  // lo <= key < hi
 }
 
-template <bool GATE>  // the gated epilogue is an instance of its own: code the common kernel does not carry
+// The gated epilogue and the one that also stores copies of the output are instances of their own: code the
+// common kernel does not carry.
+template <bool GATE, bool COPIES>
 __global__ void __launch_bounds__(PairCfg::THREADS, 1)
     sdpa_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -169,7 +171,13 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
     uint64_t* o_full = p_half + 4;   // one phase per tile: the tile's last O += P V has completed
     uint64_t* o_empty = o_full + 2;  // one phase per tile: the epilogue warps have read O out
     uint64_t* turn = o_empty + 2;    // one phase per union key block: the pipeline's softmax warps are past it
-    uint64_t* fin = turn + 2;        // one phase per tile: the softmax warps have published row sums and maxima
+    // fin[2 * s + (tile & 1)], one phase per second tile: the softmax warps have published the tile's row sums
+    // and maxima.  Two barriers per pipeline, used in turn, because a tile of one key block needs no
+    // O += P V to finish: with one barrier the softmax warps could complete it for tile n + 1 while a slow
+    // epilogue (stores held up) still waits for tile n's completion — and a parity wait cannot tell "twice"
+    // from "not yet".  They cannot reach tile n + 2 before the epilogue has taken tile n (the first O += P V
+    // of tile n + 1 waits for that), so two are enough.
+    uint64_t* fin = turn + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARS);
     uint32_t* abort_slot = tmem_slot + 1;
     float2* fin_vals = reinterpret_cast<float2*>(tmem_slot + 4);  // [tile parity 2][pipeline 2][row 128] (row sum, row maximum)
@@ -191,7 +199,8 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
             mbar_init(&o_full[s], 1);
             mbar_init(&o_empty[s], 128);
             mbar_init(&turn[s], 128);
-            mbar_init(&fin[s], 128);
+            mbar_init(&fin[2 * s], 128);
+            mbar_init(&fin[2 * s + 1], 128);
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(&k_full[s], 1);
@@ -434,7 +443,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                 if (pw.hi_of(s) == pw.lo_of(s)) {
                     // Nothing visible for this tile: zero output.
                     if (store) {
-                        for (int c = -1; c < p.n_copies; ++c) {
+                        for (int c = -1; c < (COPIES ? p.n_copies : 0); ++c) {
                             uint4* dst = reinterpret_cast<uint4*>((c < 0 ? p.out : reinterpret_cast<uint16_t*>(p.out_copies[c])) + eoff);
                             for (int i = 0; i < HD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
                         }
@@ -443,7 +452,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                     continue;
                 }
                 const int tq = s ? tq1 : tq0;
-                if (!mbar_wait_relaxed_warp<2>(&fin[s], tq & 1)) {
+                if (!mbar_wait_relaxed_warp<2>(&fin[2 * s + (tq & 1)], (tq >> 1) & 1)) {
                     report_fault(p.fault, FAULT_WAIT_FULL, 0x500u + s);
                     ok = false;
                     break;
@@ -490,7 +499,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                                 }
                             }
                             store_bf16x16(dst + c * 32 + i * 16, w8);
-                            if (p.n_copies) store_copies_bf16x16(p.out_copies, p.n_copies, eoff + c * 32 + i * 16, w8);
+                            if (COPIES) store_copies_bf16x16(p.out_copies, p.n_copies, eoff + c * 32 + i * 16, w8);
                         }
                     }
                 }
@@ -650,17 +659,9 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
                 mbar_arrive(&turn[s]);
                 if (act && j + 1 == hi) {
                     // The tile's last key block is on its way: hand the row sum and maximum to the
-                    // epilogue warps and go on with the next tile.  Not before the epilogue has taken the
-                    // previous tile, though: a tile of one key block needs no O += P V to get here, so these
-                    // warps could complete `fin` twice while a slow epilogue (its stores held up) still waits
-                    // for the first completion — which a parity wait can then no longer tell from "not yet".
-                    if (tq > 0 && !mbar_wait_warp<3>(&o_empty[s], (tq - 1) & 1)) {
-                        report_fault(p.fault, FAULT_WAIT_EMPTY, 0x600u + s);
-                        ok = false;
-                        break;
-                    }
+                    // epilogue warps and go on with the next tile.
                     fin_vals[((tq & 1) * 2 + s) * 128 + r] = make_float2(l, m);
-                    mbar_arrive(&fin[s]);
+                    mbar_arrive(&fin[2 * s + (tq & 1)]);
                     ++tq;
                 }
             }
