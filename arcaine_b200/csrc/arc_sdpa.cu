@@ -132,8 +132,10 @@ static int device_state(DeviceState** out) {
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<128, 2>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 1>, s.smem_optin - kDecodeStaticSmem));
             ARC_CUDA(opt_in_smem(sdpa_decode_kernel<256, 2>, s.smem_optin - kDecodeStaticSmem));
-            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<128>, kMergeSmemOptin));
-            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<256>, kMergeSmemOptin));
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<128, false>, kMergeSmemOptin));
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<256, false>, kMergeSmemOptin));
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<128, true>, kMergeSmemOptin));
+            ARC_CUDA(opt_in_smem(sdpa_decode_merge_kernel<256, true>, kMergeSmemOptin));
             s.ready.store(true, std::memory_order_release);
         }
     }
@@ -542,11 +544,15 @@ static int launch_decode(const arc_sdpa_decode_params* p, const DecodePlan& plan
     mp.x_wait_cycles = p->xchg_wait_cycles > 0 ? p->xchg_wait_cycles : 2000000000LL;
     mp.fault = ds->fault;
     dim3 mgrid((unsigned)p->nq, (unsigned)p->batch, 1);
+    const bool xchg = mp.x_world > 1;
     if (empty_cache) {
-        sdpa_decode_merge_kernel<HD><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
+        if (xchg) sdpa_decode_merge_kernel<HD, true><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
+        else sdpa_decode_merge_kernel<HD, false><<<mgrid, MERGE_THREADS, plan.merge_smem, stream>>>(mp);
         ARC_CUDA(cudaGetLastError());
+    } else if (xchg) {
+        ARC_CUDA(launch_dependent(sdpa_decode_merge_kernel<HD, true>, mgrid, dim3(MERGE_THREADS), plan.merge_smem, stream, mp));
     } else {
-        ARC_CUDA(launch_dependent(sdpa_decode_merge_kernel<HD>, mgrid, dim3(MERGE_THREADS), plan.merge_smem, stream, mp));
+        ARC_CUDA(launch_dependent(sdpa_decode_merge_kernel<HD, false>, mgrid, dim3(MERGE_THREADS), plan.merge_smem, stream, mp));
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return ARC_OK;

@@ -488,7 +488,10 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* scrat
     return r;
 }
 
-template <int HD>
+// XCHG: the instance that also exchanges records with other GPUs.  It keeps every source's values in
+// registers; the plain merge — hundreds of small blocks for a large batch — stays lean enough for five blocks
+// per SM.
+template <int HD, bool XCHG>
 __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const DecodeMergeParams p) {
     extern __shared__ uint8_t smem_raw[];
     long long* cum = reinterpret_cast<long long*>(smem_raw);
@@ -598,7 +601,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
         a1 *= inv;
         if (p.out_f32) *reinterpret_cast<float2*>(p.out_f32 + row * HD + d) = make_float2(a0, a1);
     }
-    if (p.x_world > 1) {
+    if (XCHG && p.x_world > 1) {
         // Sequence-sharded: this rank's (out, lse) of the row goes straight into every rank's exchange
         // buffer over NVLink as plain peer stores of (value, step) words.  Then the block waits — for a
         // bounded time — until the words of every source rank show this step, and folds the records.
