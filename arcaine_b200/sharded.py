@@ -227,12 +227,12 @@ class SeqShardedDecode:
             self.step += 1
             return ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, gate=gate, out=self.out,
                                    exchange=(self._peers, self.world, self.rank, self.step))
+        if self.world == 1:  # nothing to exchange: the plain decode call
+            return ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, gate=gate, out=self.out)
         ops.sdpa_decode(q, k_local, v_local, scale=scale, kv_len=kv_len, return_partial=True, want_out=False,
                         partial_out=self.part_out, partial_lse=self.part_lse)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
-            return ops.sdpa_merge(self.all_out, self.all_lse, gate=gate, out=self.out)
-        return ops.sdpa_merge(self.part_out.unsqueeze(0), self.part_lse.unsqueeze(0), gate=gate, out=self.out)
+        dist.all_gather_into_tensor(self.gathered.view(-1), self.record, group=self.group)
+        return ops.sdpa_merge(self.all_out, self.all_lse, gate=gate, out=self.out)
 
 
 class GatheredPrefill:
