@@ -923,6 +923,16 @@ def run_reference_arm(args):
         "e2e": {"value": round(value, 6), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if args.workload in ("prefill_window", "canvas"):
+        # the two library CPU paths on the same sample, beside the port this arm reports: a reader who wants
+        # the ratio against the fastest CPU implementation finds it here
+        try:
+            others = cpu_library_baselines(args.workload)
+            if others:
+                line["cpu_baseline"]["others"] = others
+                line["cpu_baseline"]["fastest"] = max(others, key=lambda k: others[k]["value"])
+        except Exception as e:
+            line["cpu_baseline"]["others_error"] = repr(e)
     print(json.dumps(line), flush=True)
 
 
