@@ -304,6 +304,7 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
     kp.num_splits = plan.splits;
     kp.group = p->nq / p->nkv;
     kp.group_shift = -1;
+    kp.tail_base = -1;
     for (int sh = 0; sh < 31; ++sh)
         if ((1 << sh) == kp.group) kp.group_shift = sh;
 
@@ -325,7 +326,13 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
         // the same rows as 1024 single tiles are 7: the single-tile kernel is then faster).
         const long long single_tiles = (long long)plan.q_tiles * p->nq * p->batch;
         const long long sms = ds->sm_count;
-        const double cost_pair = 1.7 * (double)((pair_tiles + sms - 1) / sms);
+        // The pairs left over after the last whole wave of CTAs are cut into their two heads when every SM then
+        // gets at most one of them: a second launch (the one-tile kernel, one CTA per tile, scheduled behind this
+        // one as SMs free up) takes them, and no SM runs a whole pair while the others idle.  A single tile
+        // costs about one tile of the one-tile kernel.
+        const long long full_waves = pair_tiles / sms, left = pair_tiles - full_waves * sms;
+        const bool cut_tail = head_pair && full_waves > 0 && left > 0 && 2 * left <= sms;
+        const double cost_pair = cut_tail ? 1.7 * (double)full_waves + 1.05 : 1.7 * (double)((pair_tiles + sms - 1) / sms);
         const double cost_single = (double)((single_tiles + sms - 1) / sms);
         const bool use_pair = forced == 2 || (forced == 0 && cost_pair <= cost_single);
         if (use_pair) {
@@ -333,8 +340,9 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             kp.head_pair = head_pair ? 1 : 0;
             kp.cur_heads = head_pair ? p->nq / 2 : p->nq;
             kp.q_tiles = head_pair ? plan.q_tiles : (p->seq + 255) / 256;
-            kp.total_tiles = (int)pair_tiles;
-            const unsigned ctas = (unsigned)(pair_tiles < ds->sm_count ? pair_tiles : ds->sm_count);
+            const long long pair_units = cut_tail ? full_waves * sms : pair_tiles;
+            kp.total_tiles = (int)pair_units;
+            const unsigned ctas = (unsigned)(pair_units < ds->sm_count ? pair_units : ds->sm_count);
             if (kp.n_copies > 0) {
                 if (kp.gate) sdpa_prefill_pair_kernel<true, true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
                 else sdpa_prefill_pair_kernel<false, true><<<ctas, PairCfg::THREADS, PairCfg::SMEM_BYTES, stream>>>(tq, tk, tv, kp);
@@ -345,6 +353,21 @@ static int launch_prefill(const arc_sdpa_prefill_params* p, const PrefillPlan& p
             }
             g_launches.fetch_add(1, std::memory_order_relaxed);
             ARC_CUDA(cudaGetLastError());
+            if (cut_tail) {
+                PrefillParams tp = kp;
+                tp.head_pair = 0;
+                tp.cur_heads = p->nq;
+                tp.q_tiles = plan.q_tiles;
+                tp.tail_base = (int)pair_units;
+                tp.total_tiles = (int)(2 * left);
+                tp.num_splits = 1;
+                const dim3 grid((unsigned)(2 * left)), block(PrefillCfg<128>::THREADS);
+                if (tp.gate)
+                    ARC_CUDA(launch_dependent(sdpa_prefill_kernel<128, false, true>, grid, block, (size_t)PrefillCfg<128>::SMEM_BYTES, stream, tq, tk, tv, tp));
+                else
+                    ARC_CUDA(launch_dependent(sdpa_prefill_kernel<128, false, false>, grid, block, (size_t)PrefillCfg<128>::SMEM_BYTES, stream, tq, tk, tv, tp));
+                g_launches.fetch_add(1, std::memory_order_relaxed);
+            }
             return ARC_OK;
         }
     }

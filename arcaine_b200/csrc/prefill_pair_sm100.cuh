@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
     uint32_t* abort_slot = tmem_slot + 1;
     float2* fin_vals = reinterpret_cast<float2*>(tmem_slot + 4);  // [tile parity 2][pipeline 2][row 128] (row sum, row maximum)
 
+    grid_launch_dependents();  // a launch behind this one (the single-head tail of the unit list) may be scheduled as SMs free up
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 

@@ -53,6 +53,9 @@ struct PrefillParams {
     int head_pair;    // prefill_pair_sm100.cuh: 1 = the CTA's two tiles are the same tokens of two heads of one KV group
     int group;        // nq / nkv
     int group_shift;  // log2(group) if it is a power of two, else -1
+    // >= 0 (one-tile kernel): the launch covers the tail of a two-tile launch's unit list — tile w is head (w & 1)
+    // of the head pair with unit index tail_base + (w >> 1), one tile per CTA; -1: the plain tile list
+    int tail_base;
 };
 
 // One CTA per SM, persistent: it takes tiles (128 query tokens of one query head) round-robin
@@ -267,6 +270,15 @@ struct TileCursor {
     __device__ __forceinline__ void init(const PrefillParams& p, int first, int step_) {
         w = first;
         step = step_;
+        if (p.tail_base >= 0) {  // (the grid holds one CTA per tile: the strides below are never used)
+            const int idx = p.tail_base + (w >> 1);
+            qt = idx % p.q_tiles;
+            const int prest = idx / p.q_tiles, pairs = p.cur_heads >> 1;
+            h = (prest % pairs) * 2 + (w & 1);
+            z = prest / pairs;
+            dqt = dh = dz = 0;
+            return;
+        }
         qt = w % p.q_tiles;
         const int rest = w / p.q_tiles;
         h = rest % p.cur_heads;

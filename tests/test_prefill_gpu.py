@@ -132,6 +132,14 @@ def test_output_copies_are_written_by_every_epilogue(ops, case):
         assert torch.equal(w[:, nq:], plain) and (w[:, :nq].float() == 9.0).all()
 
 
+@pytest.mark.parametrize("gate", [False, True])
+def test_two_tile_launch_with_a_single_head_tail(ops, gate):
+    """13 token tiles x 16 head pairs = 208 two-tile units on 148 SMs: one whole wave of pairs, and the 60 pairs
+    left over are cut into 120 single heads that a second launch (the one-tile kernel, one CTA per tile) takes
+    behind the first.  Every row must come out exactly once, from either launch."""
+    run_case(ops, 1664, 1664, 32, 16, 128, 128 ** -0.5, 3, 300, seed=800, gate=gate, lse=True)
+
+
 def test_gate_epilogue_and_split_gate(ops):
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True)
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True, num_splits=2)
