@@ -114,7 +114,23 @@ __global__ void __launch_bounds__(288, 1)
     grid_launch_dependents();  // the merge kernel may be scheduled now; it waits for this grid before reading
     // A fault recorded by an earlier CTA or launch: do not start new waits.
     __shared__ uint32_t abort_flag;
-    if (threadIdx.x == 0) abort_flag = *reinterpret_cast<volatile uint32_t*>(p.fault);
+    // Everything the prologue reads from global memory is asked for at once: after an L2 flush each of these is
+    // an HBM round trip, and taken one after the other (status word and lengths, then row offsets, then the
+    // descriptors at the first copy) they kept the first K / V request waiting for several microseconds.
+    if (p.kv_row_offset)
+        for (int b = threadIdx.x * 16; b < p.batch; b += blockDim.x * 16) prefetch_l2(p.kv_row_offset + b);
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (threadIdx.x == 0) {
+        abort_flag = *reinterpret_cast<volatile uint32_t*>(p.fault);
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], ncw);
+        }
+        fence_mbar_init();
+    }
     build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
     if (abort_flag != 0u) return;
     // Lengths and row offsets live on the device, so this is where they can be checked: a sequence
@@ -135,15 +151,7 @@ __global__ void __launch_bounds__(288, 1)
     const long long g0 = (long long)blockIdx.x * per;
     const long long g1 = min(total, g0 + per);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], ncw);
-        }
-        fence_mbar_init();
-    }
-    __syncthreads();
-    if (g0 >= g1) return;
+    if (g0 >= g1) return;  // (the barriers were set up before the prefix's block-wide syncs)
 
     int b_first = 0;
     while (b_first < p.batch - 1 && cum[b_first + 1] <= g0) ++b_first;
