@@ -111,3 +111,34 @@ def test_qkv_prepare_argument_validation_needs_no_gpu():
     assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_ERR_ALIGNMENT
     p = params(q=base, q_stride_t=128)
     assert lib.arc_qkv_prepare(ctypes.byref(p), None) == _lib.ARC_ERR_BAD_SHAPE
+
+
+def test_ctypes_mirrors_have_the_layout_the_header_declares(tmp_path):
+    """The Python mirrors of the parameter structs against the C compiler's view of include/arc_sdpa.h:
+    same size, same offset for every field (a field added to one side only would shift everything behind
+    it without any error at the call)."""
+    import ctypes as C
+    import shutil
+    import subprocess
+    from arcaine_b200 import _lib
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    pairs = [("arc_sdpa_prefill_params", _lib.PrefillParams), ("arc_sdpa_decode_params", _lib.DecodeParams),
+             ("arc_qkv_prepare_params", _lib.QkvPrepareParams), ("arc_head_shard", _lib.HeadShard)]
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "arc_sdpa.h"', 'int main(void) {']
+    for cname, mirror in pairs:
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for fname, _ in mirror._fields_:
+            lines.append(f'  printf("{cname}.{fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    include = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    subprocess.run([cc, "-I", include, "-o", str(exe), str(src)], check=True)
+    seen = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, mirror in pairs:
+        assert int(seen[cname]) == C.sizeof(mirror), cname
+        for fname, _ in mirror._fields_:
+            assert int(seen[f"{cname}.{fname}"]) == getattr(mirror, fname).offset, f"{cname}.{fname}"
