@@ -507,7 +507,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) sdpa_decode_merge_kernel(const 
     float* acc_sm = red + 8;                                        // (warps) x HD
     float* wgt = acc_sm + (MERGE_THREADS / 32) * HD;                // one weight per record
     __shared__ int n_live_sm;
-    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);  // independent of the decode kernel's results
+    // What does not depend on the decode kernel's results happens while it still runs: the length prefix, and
+    // requests for the lines the tail will need (this row's gate values, the status word) into L2.
+    if (p.gate && p.out && threadIdx.x < HD * 2 / 128)
+        prefetch_l2(p.gate + (long long)blockIdx.y * p.o_stride_b + (long long)blockIdx.x * HD + threadIdx.x * 64);
+    if (threadIdx.x == 32) prefetch_l2(p.fault);
+    build_len_prefix(p.kv_len, p.kv_len_uniform, p.batch, cum);
     grid_dependency_wait();                                        // from here on its partial records are read
     if (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) return;  // block-uniform: a status is set, no work
     const int h = blockIdx.x, b = blockIdx.y;
