@@ -20,8 +20,10 @@
 //     O^T (hd x 8 heads)     += V_tile^T (hd x 16) * P^T (16 x 8)
 // Online softmax state (max, sum) is per head = per accumulator column pair,
 // reduced across the key rows with warp shuffles.  Each (CTA, sequence) pair a
-// share touches yields one partial (normalised out, lse) record per slice; the
-// merge kernel folds them and applies the optional sigmoid output gate
+// share touches yields partial (normalised out, lse) records: one per slice, or —
+// for the last segment of a share, which is most of them — one for the CTA, the
+// slices folded through shared memory first; the merge kernel folds the records
+// and applies the optional sigmoid output gate
 // (src/modeling/qwen3_5_moe/kernels.hpp:80-88) while writing bf16.
 //
 // The reference kernels this replaces read K/V once per query head and never

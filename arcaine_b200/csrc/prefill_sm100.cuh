@@ -64,8 +64,11 @@ struct PrefillParams {
 // tile's output.  The score accumulator is
 // multi-buffered in tensor memory (S0, S1[, S2], then O), so S = Q K^T runs one or two key
 // blocks ahead of the softmax; eight softmax warps (two threads per query row, 64 keys
-// each) look at the next block's maximum before they exponentiate the current one, which
-// hides the exchange of row maxima.  Eight rather than sixteen softmax warps on purpose: the
+// each).  With three score buffers (head dim 128) they look at the next block's maximum
+// before they exponentiate the current one, which hides the exchange of row maxima; with
+// two (head dim 256) every block is taken on its own, because the next block's scores
+// cannot be computed before this block's probabilities have been consumed.
+// Eight rather than sixteen softmax warps on purpose: the
 // single MMA-issuing thread shares an instruction scheduler with them, and with four busy
 // warps per scheduler it could not issue MMAs fast enough to keep the tensor pipe fed.
 template <int HD>
