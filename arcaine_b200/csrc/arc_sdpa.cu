@@ -227,11 +227,15 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, const in
     int splits = p->num_splits;
     const long long tiles = (long long)plan->q_tiles * p->nq * p->batch;
     if (splits == 0) {
-        // Split the key range only when the tiles alone leave most SMs idle.
+        // Split the key range only when the tiles alone leave most SMs idle and there are enough key blocks
+        // to pay for folding the parts again (measured: about 8 us for the fold against 1.3-2 us per key
+        // block; with fewer than ten blocks a tile is faster in one piece, and more than eight parts cost
+        // more than they save).
         splits = 1;
-        if (tiles * 2 <= sm_count && kv_blocks >= 4) {
+        if (tiles * 2 <= sm_count && kv_blocks >= 10) {
             splits = (int)(sm_count / tiles);
             if (splits > kv_blocks / 2) splits = kv_blocks / 2;
+            if (splits > 8) splits = 8;
             if (splits < 1) splits = 1;
         }
     }
@@ -240,15 +244,16 @@ static int plan_prefill(const arc_sdpa_prefill_params* p, int sm_count, const in
     // A split the library chose itself is run as a thread-block cluster where the device allows it: the
     // CTAs of a tile fold their accumulators through distributed shared memory in the same launch, no
     // partial records, no merge kernel, no workspace.  An explicit num_splits keeps the two-launch form.
-    // The cluster size is the largest power of two within the split count for which all tiles' clusters
-    // are resident at once (clusters are placed inside one GPC each, so fewer fit than SMs / size suggests;
-    // a second wave would double the time).
-    if (p->num_splits == 0 && splits > 1 && active_clusters && p->mask_type != ARC_MASK_EXPLICIT) {
-        int cs = 0;
-        for (int c = 2, lg = 1; c <= 8 && c <= splits; c *= 2, ++lg)
-            if (active_clusters[lg] >= tiles) cs = c;
-        if (cs > 0) {
-            plan->cluster = cs;
+    // All tiles' clusters must be resident at once (clusters are placed inside one GPC each, so fewer fit
+    // than SMs / size suggests; a second wave would double the time).  Head dim 256 only: at head dim 128 the two-launch form measured
+    // 5-7 us faster (the cluster instance of that kernel does not fit its register budget without spills).
+    if (p->num_splits == 0 && (splits == 2 || splits == 4) && p->hd == 256 && active_clusters &&
+        p->mask_type != ARC_MASK_EXPLICIT) {
+        // (two or four parts: with eight, a CTA reads seven eighths of its rows from the others and the
+        // two-launch form measured 2-3 us faster; three parts would have to become two)
+        const int lg = splits == 2 ? 1 : 2;
+        if (active_clusters[lg] >= tiles) {
+            plan->cluster = splits;
             splits = 1;
         }
     }

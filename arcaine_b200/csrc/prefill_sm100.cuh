@@ -89,7 +89,7 @@ struct PrefillCfg {
     static constexpr int SMEM_BYTES = (1 + K_STAGES + V_STAGES) * TILE_BYTES + NUM_BARS * 8 + 16 + XCH_FLOATS * 4 + 1024;
     static constexpr int SOFTMAX_WARPS = 8;
     static constexpr int THREADS = 32 * (SOFTMAX_WARPS + 2);
-    static constexpr int MAX_REGS = 168;  // 65536 registers over 12 allocated warps
+    static constexpr int MAX_REGS = 168;  // ten warps put three on some scheduler: 3 x 32 x 168 fits its 16384 registers, 176 does not
 };
 
 // Per-row visibility for blocks that need element masking.

@@ -96,8 +96,9 @@ def test_key_range_splits_agree(ops, splits):
     (200, 517, 6, 2, 3, 300),                # ragged in both directions
 ])
 def test_cluster_fold_of_key_range_splits(ops, hd, seq, kv_len, nq, nkv, mask_type, window):
-    """Splits the library chooses itself run as one thread-block cluster per tile whose CTAs fold their
-    accumulators through distributed shared memory; with the gate and the log-sum-exp output."""
+    """Splits the library chooses itself: at head dim 256 one thread-block cluster per tile whose CTAs fold
+    their accumulators through distributed shared memory, at head dim 128 partial records and a merge launch;
+    with the gate and the log-sum-exp output."""
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=500 + hd + seq, gate=True, lse=True)
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=600 + hd + seq)
 
