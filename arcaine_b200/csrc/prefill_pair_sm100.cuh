@@ -186,11 +186,15 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    if (threadIdx.x == 0) *abort_slot = (*reinterpret_cast<volatile uint32_t*>(p.fault) != 0u) ? 1u : 0u;
-    __syncthreads();
-    if (*abort_slot) return;
-
+    // After an L2 flush the status word, the three descriptors and the first tiles are an HBM round trip each:
+    // the descriptors and the status word are requested at once, and the barriers are set up while they travel.
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
     if (threadIdx.x == 0) {
+        const uint32_t fault_word = *reinterpret_cast<volatile uint32_t*>(p.fault);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&q_full[s], 1);
             mbar_init(&q_empty[s], 1);
@@ -212,7 +216,10 @@ __global__ void __launch_bounds__(PairCfg::THREADS, 1)
             mbar_init(&v_empty[s], 2);
         }
         fence_mbar_init();
+        *abort_slot = fault_word != 0u ? 1u : 0u;
     }
+    __syncthreads();
+    if (*abort_slot) return;
     if (warp == C::PRODUCER_WARP) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
         tmem_relinquish();
