@@ -1068,6 +1068,11 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
     tc_fence_before_sync();
     __syncthreads();
     if (warp == PRODUCER_WARP) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    // A launch that covers the tail of a two-tile launch's unit list runs beside that launch (programmatic
+    // stream serialization) and reads nothing it writes — but whatever follows in the stream waits for this
+    // grid only, so this grid does not complete before the one in front of it has: every CTA ends on the
+    // grid-dependency wait (a no-op for launches without the attribute).
+    if (p.tail_base >= 0) grid_dependency_wait();
     // A CTA's shared memory may be read by the others only while it is alive: nobody leaves before the
     // whole cluster is through (all threads are still running here).
     if constexpr (CLUSTER) cluster_sync_all();

@@ -141,6 +141,22 @@ def test_two_tile_launch_with_a_single_head_tail(ops, gate):
     run_case(ops, 1664, 1664, 32, 16, 128, 128 ** -0.5, 3, 300, seed=800, gate=gate, lse=True)
 
 
+def test_consumer_right_behind_the_two_launch_form_sees_finished_rows(ops):
+    """The single-head tail runs beside the two-tile launch in front of it; what follows in the stream waits for
+    the tail launch only, so the tail must not complete first.  A copy enqueued right behind the call, with no
+    host synchronisation in between, has to see every row."""
+    q, k, v = seeded_bf16(1664, 32, 128, seed=810).cuda(), seeded_bf16(1664, 16, 128, seed=811).cuda(), \
+        seeded_bf16(1664, 16, 128, seed=812).cuda()
+    ref = ops.sdpa_prefill(q, k, v, scale=128 ** -0.5, mask_type=ops.MASK_CAUSAL, window=300).clone()
+    torch.cuda.synchronize()
+    for _ in range(20):
+        out = torch.zeros_like(ref)
+        ops.sdpa_prefill(q, k, v, scale=128 ** -0.5, mask_type=ops.MASK_CAUSAL, window=300, out=out)
+        snap = out.clone()
+        torch.cuda.synchronize()
+        assert torch.equal(snap, ref)
+
+
 def test_gate_epilogue_and_split_gate(ops):
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True)
     run_case(ops, 150, 400, 6, 2, 256, 0.0625, 3, oracle.INT_MAX, seed=41, gate=True, num_splits=2)
