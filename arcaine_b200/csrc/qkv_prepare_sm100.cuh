@@ -84,7 +84,10 @@ __device__ __forceinline__ float bf16_rne(float x) {
 // eight warps even when a rank holds only a few heads).
 // QWEN: the Qwen3.5 form (pairs rot_half apart, per-axis positions, V copied); the common instance does not
 // carry its branches.
-template <int HD, bool QWEN>
+// AHEAD: a warp issues the loads of its next pass before it works on this one (64 registers, four CTAs per SM:
+// faster when a token has many rows); without it 40 registers and six CTAs per SM (faster for the few rows per
+// token of a rank that holds a few heads).
+template <int HD, bool QWEN, bool AHEAD>
 __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams p, const int tpc) {
     constexpr int LPR = HD / 16;    // lanes per row
     constexpr int RPW = 32 / LPR;   // rows per warp and pass
@@ -151,43 +154,68 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(const QkvPrepareParams
         __syncthreads();
         const float inv_rows = 1.0f / static_cast<float>(rows);
         const int slots = tpc * rows;  // (token in round, row) pairs of this round
-        for (int r0 = warp * RPW; r0 < slots; r0 += 8 * RPW) {
+        // AHEAD: the addresses of the next pass's rows are worked out and their loads issued before this pass's
+        // rows are processed, so that a warp has two passes' worth of loads in flight instead of waiting out one
+        // DRAM latency per pass.
+        struct Pass {
+            const uint16_t* weight;
+            uint16_t* dst;
+            uint4 rl, rh;
+            int tl;
+            bool valid, rope, norm;
+        };
+        auto fetch = [&](int r0) -> Pass {
+            Pass f;
             const int slot = r0 + sub;
-            const int tl = static_cast<int>((static_cast<float>(slot) + 0.5f) * inv_rows);  // exact: slot < 2^20
-            const int r = slot - tl * rows;
-            const int tk = tk0 + tl;
-            const bool valid = slot < slots && tk < tokens;
-            const int b = valid ? s_tok[2 * tl] : 0;
-            const int t = valid ? s_tok[2 * tl + 1] : 0;
+            f.tl = static_cast<int>((static_cast<float>(slot) + 0.5f) * inv_rows);  // exact: slot < 2^20
+            const int r = slot - f.tl * rows;
+            const int tk = tk0 + f.tl;
+            f.valid = slot < slots && tk < tokens;
+            const int b = f.valid ? s_tok[2 * f.tl] : 0;
+            const int t = f.valid ? s_tok[2 * f.tl + 1] : 0;
             const uint16_t* src = nullptr;
-            uint16_t* dst = nullptr;
-            const uint16_t* weight = nullptr;
-            bool rope = false, norm = true;
-            if (valid) {
+            f.dst = nullptr;
+            f.weight = nullptr;
+            f.rope = false;
+            f.norm = true;
+            if (f.valid) {
                 if (r < rows_q) {
-                    src = dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
-                    weight = p.q_weight;
-                    rope = true;
+                    src = f.dst = p.q + b * p.q_stride_b + t * p.q_stride_t + (long long)r * HD;
+                    f.weight = p.q_weight;
+                    f.rope = true;
                 } else if (r < rows_q + rows_k) {
                     const int h = r - rows_q;
                     src = p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
-                    dst = p.k_dst + b * p.kd_stride_b + t * p.kd_stride_t + (long long)h * HD;
-                    weight = p.k_weight;
-                    rope = true;
+                    f.dst = p.k_dst + b * p.kd_stride_b + t * p.kd_stride_t + (long long)h * HD;
+                    f.weight = p.k_weight;
+                    f.rope = true;
                 } else {
                     const int h = r - rows_q - rows_k;
                     src = p.v_src ? p.v_src + b * p.vs_stride_b + t * p.vs_stride_t + (long long)h * HD
                                   : p.k_src + b * p.ks_stride_b + t * p.ks_stride_t + (long long)h * HD;
-                    dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
-                    norm = !(QWEN && p.v_copy);
+                    f.dst = p.v_dst + b * p.vd_stride_b + t * p.vd_stride_t + (long long)h * HD;
+                    f.norm = !(QWEN && p.v_copy);
                 }
             }
-            float lo[8], hi[8];
-            uint4 rl = make_uint4(0u, 0u, 0u, 0u), rh = rl;
-            if (valid) {
-                rl = *reinterpret_cast<const uint4*>(src + li * 8);
-                rh = *reinterpret_cast<const uint4*>(src + HD / 2 + li * 8);
+            f.rl = make_uint4(0u, 0u, 0u, 0u);
+            f.rh = f.rl;
+            if (f.valid) {
+                f.rl = *reinterpret_cast<const uint4*>(src + li * 8);
+                f.rh = *reinterpret_cast<const uint4*>(src + HD / 2 + li * 8);
             }
+            return f;
+        };
+        Pass nxt;
+        if (AHEAD) nxt = fetch(warp * RPW);
+        for (int r0 = warp * RPW; r0 < slots; r0 += 8 * RPW) {
+            const Pass cur = AHEAD ? nxt : fetch(r0);
+            if (AHEAD && r0 + 8 * RPW < slots) nxt = fetch(r0 + 8 * RPW);
+            const bool valid = cur.valid, rope = cur.rope, norm = cur.norm;
+            const int tl = cur.tl;
+            const uint16_t* weight = cur.weight;
+            uint16_t* dst = cur.dst;
+            const uint4 rl = cur.rl, rh = cur.rh;
+            float lo[8], hi[8];
             unpack8(rl, lo);
             unpack8(rh, hi);
             float ss = 0.f;
