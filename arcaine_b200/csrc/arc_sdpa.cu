@@ -38,7 +38,7 @@ struct DeviceState {
     int sm_count = 0;
     int smem_optin = 0;
     // largest cluster size (2, 4 or 8; 0 = none) the cluster form of the prefill kernel can be launched with, per head dim
-    // [head dim 128 / 256][log2(cluster size)]: how many clusters of 2, 4, 8 CTAs of the cluster form of the
+    // [head dim 128 / 256][log2(cluster size)]: how many clusters of 2 or 4 CTAs of the cluster form of the
     // prefill kernel the device can hold at once (0: that size cannot be launched)
     int active_clusters[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 };
@@ -110,7 +110,7 @@ static int device_state(DeviceState** out) {
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<128, false, false, true>, PrefillCfg<128>::SMEM_BYTES));
             ARC_CUDA(opt_in_smem(sdpa_prefill_kernel<256, false, false, true>, PrefillCfg<256>::SMEM_BYTES));
             for (int hi = 0; hi < 2; ++hi) {
-                for (int cs = 2, lg = 1; cs <= 8; cs *= 2, ++lg) {
+                for (int cs = 2, lg = 1; cs <= 4; cs *= 2, ++lg) {
                     cudaLaunchConfig_t cfg{};
                     cfg.gridDim = dim3((unsigned)(s.sm_count / cs * cs));  // the answer is capped by the grid asked about
                     cfg.blockDim = dim3(hi ? PrefillCfg<256>::THREADS : PrefillCfg<128>::THREADS);

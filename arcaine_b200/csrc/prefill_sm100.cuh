@@ -751,9 +751,8 @@ __global__ void __maxnreg__(PrefillCfg<HD>::MAX_REGS)
                 fence_acq_rel_cluster();
                 for (int c = 0; c < csize; ++c) mbar_arrive_cluster(map_to_cta(pr, c));
             }
-            if (csize == 2) fold_rows(tw, std::integral_constant<int, 2>{});
-            else if (csize == 4) fold_rows(tw, std::integral_constant<int, 4>{});
-            else fold_rows(tw, std::integral_constant<int, 8>{});
+            if (csize == 2) fold_rows(tw, std::integral_constant<int, 2>{});  // the host launches clusters of 2 or 4
+            else fold_rows(tw, std::integral_constant<int, 4>{});
             // every softmax thread of this CTA is done reading the cluster's shared memory
             softmax_sync();
             if (threadIdx.x == 0) {

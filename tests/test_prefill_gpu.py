@@ -88,18 +88,22 @@ def test_key_range_splits_agree(ops, splits):
 
 
 @pytest.mark.parametrize("hd", [128, 256])
-@pytest.mark.parametrize("seq,kv_len,nq,nkv,mask_type,window", [
-    (130, 2100, 4, 2, 0, oracle.INT_MAX),    # 8 tiles, 17 key blocks: clusters of 8, ragged last tile
-    (130, 2100, 4, 2, 3, 100),               # the same with a window: most CTAs of a cluster see no key
-    (256, 1200, 8, 4, 3, oracle.INT_MAX),    # 16 tiles, 10 key blocks: clusters of 4
-    (256, 700, 24, 4, 0, oracle.INT_MAX),    # 48 tiles, 6 key blocks: clusters of 2
-    (200, 517, 6, 2, 3, 300),                # ragged in both directions
+@pytest.mark.parametrize("seq,kv_len,nq,nkv,mask_type,window,parts", [
+    (256, 1300, 28, 4, 0, oracle.INT_MAX, 2),   # 56 tiles on 148 SMs, 11 key blocks: two parts
+    (200, 1300, 28, 4, 3, 300, 2),              # the same ragged and windowed: CTAs of a cluster without keys
+    (256, 2100, 16, 8, 0, oracle.INT_MAX, 4),   # 32 tiles, 17 key blocks (the last one ragged): four parts
+    (130, 2100, 16, 2, 3, 100, 4),              # 32 tiles, a window: most CTAs of a cluster see no key
+    (130, 2100, 4, 2, 0, oracle.INT_MAX, 8),    # 8 tiles: eight parts, always two launches
+    (256, 1200, 8, 4, 3, oracle.INT_MAX, 5),    # 16 tiles, 10 key blocks: five parts, two launches
 ])
-def test_cluster_fold_of_key_range_splits(ops, hd, seq, kv_len, nq, nkv, mask_type, window):
-    """Splits the library chooses itself: at head dim 256 one thread-block cluster per tile whose CTAs fold
-    their accumulators through distributed shared memory, at head dim 128 partial records and a merge launch;
-    with the gate and the log-sum-exp output."""
+def test_key_range_splits_the_library_chooses(ops, hd, seq, kv_len, nq, nkv, mask_type, window, parts):
+    """Splits the library chooses itself: two or four parts at head dim 256 run as one thread-block cluster per
+    tile whose CTAs fold their accumulators through distributed shared memory (one launch); everything else as
+    partial records and a merge launch.  With the gate and the log-sum-exp output."""
+    before = ops.launch_count()
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=500 + hd + seq, gate=True, lse=True)
+    torch.cuda.synchronize()
+    assert ops.launch_count() - before == (1 if hd == 256 and parts in (2, 4) else 2)
     run_case(ops, seq, kv_len, nq, nkv, hd, hd ** -0.5, mask_type, window, seed=600 + hd + seq)
 
 
@@ -111,7 +115,7 @@ def test_output_copies_are_written_by_every_epilogue(ops, case):
     seq, kv, nq, nkv, hd, mask, win, splits = {
         "hd128": (1024, 1024, 8, 4, 128, 3, 256, 0),         # (the two-tile kernel's copies: test_prefill_pair_gpu.py)
         "single": (300, 300, 4, 2, 256, 3, oracle.INT_MAX, 1),
-        "cluster": (256, 1200, 4, 2, 256, 0, oracle.INT_MAX, 0),
+        "cluster": (256, 2100, 16, 8, 256, 0, oracle.INT_MAX, 0),    # 32 tiles, 17 key blocks: clusters of four
         "two_launch": (256, 1200, 4, 2, 128, 0, oracle.INT_MAX, 3),
         "nothing_visible": (200, 100, 4, 2, 128, 3, oracle.INT_MAX, 0),  # the first 100 queries see no key
     }[case]
